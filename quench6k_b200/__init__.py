@@ -5,5 +5,6 @@ from . import config as config            # noqa: F401  (registers nothing by it
 from .models import flint as _flint       # noqa: F401  (registers FlintForCausalLM)
 from .models import pedotar as _pedotar   # noqa: F401  (registers Pedotar)
 from .models import kipedra as _kipedra   # noqa: F401  (registers Kipedra)
+from .models import sigusun as _sigusun   # noqa: F401  (registers Sigusun)
 from .sampling.params import SamplingParams      # noqa: F401
 from .engine.engine import Engine, RequestOutput   # noqa: F401

@@ -60,6 +60,7 @@ struct FlexArgs {
     const float* talk;                  // [H, H] or null
     void* out; int out_head_major;
     int T_, H, Hkv;
+    const float* sinks;                 // [H] or null: exp(sinks[h]) joins head h's softmax denominator (no key, no value, not scaled)
 };
 
 template <typename T>
@@ -122,6 +123,12 @@ __global__ void __launch_bounds__(128) attention_flex_kernel(const FlexArgs a) {
                 }
             }
             m = mn;
+        }
+        if (a.sinks) {                                  // the sink counts once in the denominator
+            const float sk = a.sinks[h], mn = fmaxf(m, sk), corr = expf(m - mn);
+            l = l * corr + expf(sk - mn);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[i] *= corr;
         }
         const float inv = 1.0f / l;
         const size_t orow = a.out_head_major ? (size_t)h * a.T_ + t : (size_t)t * a.H + h;
@@ -295,12 +302,14 @@ __global__ void __launch_bounds__(128) qkv_pages_kernel(const float* qkv, int ld
 // The inputs of attention over a cached latent.  x: FP32 [T, ld] = [H query heads of (dim + rd) | latent of `rank` | rd].
 // Block (t, h < H): the head's first `dim` values -> qn[(h T + t) dim] (they go through the key up-projection next), its
 // last rd values, the first `turn` of them rotated -> qr[(h T + t) rd].  Block (t, H): the latent, RMS-normed with weight
-// cw -> the page row's first `rank` values; the shared rotated key part -> the row's last rd.
+// cw -> the page row's first `rank` values; the shared rotated key part -> the row's last rd.  neighbours: the rotation
+// pairs 2i with 2i+1 instead of i with i + turn/2.  A layer that reads another layer's pages has no block (t, H) (and x no
+// latent columns).
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prep_kernel(const float* x, int ld, int H, int dim, int rd, int rank, const float* cw, float eps,
-                                                          const float* inv_freq, int turn, const int* positions, const int* req_of_token,
-                                                          const int* block_table, int max_blocks, int page_size, T* qn, T* qr,
-                                                          T* pages, int T_) {
+                                                          const float* inv_freq, int turn, int neighbours, const int* positions,
+                                                          const int* req_of_token, const int* block_table, int max_blocks, int page_size,
+                                                          T* qn, T* qr, T* pages, int T_) {
     pdl_enter();
     extern __shared__ float xs[];            // rd floats (the part that turns)
     __shared__ float red[32];
@@ -311,7 +320,7 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const float* x, int ld
         for (int d = threadIdx.x; d < dim; d += blockDim.x) qn[row * dim + d] = from_f32<T>(src[d]);
         for (int d = threadIdx.x; d < rd; d += blockDim.x) xs[d] = src[dim + d];
         __syncthreads();
-        for (int d = threadIdx.x; d < rd; d += blockDim.x) qr[row * rd + d] = from_f32<T>(rotated(xs, d, turn, 0, pos, inv_freq));
+        for (int d = threadIdx.x; d < rd; d += blockDim.x) qr[row * rd + d] = from_f32<T>(rotated(xs, d, turn, neighbours, pos, inv_freq));
         return;
     }
     const float* src = x + (size_t)t * ld + (size_t)H * (dim + rd);
@@ -324,7 +333,7 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const float* x, int ld
     if (page < 0) return;
     T* dst = pages + ((size_t)page * page_size + pos % page_size) * (rank + rd);
     for (int d = threadIdx.x; d < rank; d += blockDim.x) dst[d] = from_f32<T>(src[d] * inv * cw[d]);
-    for (int d = threadIdx.x; d < rd; d += blockDim.x) dst[rank + d] = from_f32<T>(rotated(xs, d, turn, 0, pos, inv_freq));
+    for (int d = threadIdx.x; d < rd; d += blockDim.x) dst[rank + d] = from_f32<T>(rotated(xs, d, turn, neighbours, pos, inv_freq));
 }
 
 // src: FP32 [H, T, n] -> out: [T, H n] in the storage type.
@@ -345,8 +354,8 @@ __global__ void heads_to_rows_kernel(const float* src, T* out, int H, int T_, in
 Q6K_API int q6k_attention_flex(const float* qa, int da, const void* qb, int db, int q_head_major, const void* k_pages,
                                long long k_head_stride, int k_ld, const void* v_pages, long long v_head_stride, int v_ld, int dv,
                                const int* block_table, int max_blocks, int page_size, const int* req_of_token, const int* positions,
-                               int window, int chunk, float scale, const float* talk, void* out, int out_head_major, int T_, int H,
-                               int Hkv, int dtype, cudaStream_t st) {
+                               int window, int chunk, float scale, const float* talk, const float* sinks, void* out, int out_head_major,
+                               int T_, int H, int Hkv, int dtype, cudaStream_t st) {
     if (T_ == 0) return 0;
     const int dk = da + db;
     Q6K_REQUIRE(T_ > 0 && H > 0 && Hkv > 0 && H % Hkv == 0, "attention: bad head counts H=%d Hkv=%d", H, Hkv);
@@ -355,8 +364,9 @@ Q6K_API int q6k_attention_flex(const float* qa, int da, const void* qb, int db, 
     Q6K_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0, "attention: bad page_size %d / max_blocks %d / window %d / chunk %d",
                 page_size, max_blocks, window, chunk);
     FlexArgs a{qa, da, qb, db, q_head_major, k_pages, k_head_stride, k_ld, v_pages, v_head_stride, v_ld, dv, block_table, max_blocks,
-               page_size, req_of_token, positions, window, chunk, scale, talk, out, out_head_major, T_, H, Hkv};
+               page_size, req_of_token, positions, window, chunk, scale, talk, out, out_head_major, T_, H, Hkv, sinks};
     if (talk) {
+        Q6K_REQUIRE(!sinks, "attention with mixed heads takes no sinks");
         Q6K_REQUIRE(dv <= 256 && H <= 64, "attention with mixed heads: value width %d (at most 256), %d heads (at most 64)", dv, H);
         const int warps = H < 8 ? H : 8;
         const size_t smem = ((size_t)H * dk + 2 * H + (size_t)H * 32 + (size_t)H * H) * sizeof(float);
@@ -395,15 +405,15 @@ Q6K_API int q6k_qkv_pages(const float* qkv, int ld, int splits, long long split_
 }
 
 Q6K_API int q6k_latent_prep(const float* x, int ld, int T_, int H, int dim, int rd, int rank, const float* cw, float eps,
-                            const float* inv_freq, int turn, const int* positions, const int* req_of_token, const int* block_table,
-                            int max_blocks, int page_size, void* qn, void* qr, void* pages, int dtype, cudaStream_t st) {
+                            const float* inv_freq, int turn, int neighbours, const int* positions, const int* req_of_token,
+                            const int* block_table, int max_blocks, int page_size, void* qn, void* qr, void* pages, int dtype, cudaStream_t st) {
     if (T_ == 0) return 0;
-    Q6K_REQUIRE(T_ > 0 && H > 0 && dim > 0 && rd >= 0 && rank > 0, "latent_prep: bad sizes T=%d H=%d dim=%d rd=%d rank=%d", T_, H, dim, rd, rank);
+    Q6K_REQUIRE(T_ > 0 && H > 0 && dim > 0 && rd >= 0 && (rank > 0 || !pages), "latent_prep: bad sizes T=%d H=%d dim=%d rd=%d rank=%d", T_, H, dim, rd, rank);
     Q6K_REQUIRE(turn >= 0 && turn % 2 == 0 && turn <= rd && (turn == 0 || inv_freq), "latent_prep: %d turning dimensions of %d", turn, rd);
-    Q6K_REQUIRE(H + 1 <= 65535 && page_size > 0 && max_blocks > 0, "latent_prep: bad grid or pages");
+    Q6K_REQUIRE(H + 1 <= 65535 && (!pages || (page_size > 0 && max_blocks > 0 && cw)), "latent_prep: bad grid or pages");
     const size_t smem = (size_t)(rd > 0 ? rd : 1) * sizeof(float);
-    Q6K_DISPATCH(dtype, q6k_launch(latent_prep_kernel<T>, dim3(T_, H + 1), 128, smem, st, x, ld, H, dim, rd, rank, cw, eps, inv_freq, turn,
-                                   positions, req_of_token, block_table, max_blocks, page_size, (T*)qn, (T*)qr, (T*)pages, T_););
+    Q6K_DISPATCH(dtype, q6k_launch(latent_prep_kernel<T>, dim3(T_, pages ? H + 1 : H), 128, smem, st, x, ld, H, dim, rd, rank, cw, eps, inv_freq, turn,
+                                   neighbours, positions, req_of_token, block_table, max_blocks, page_size, (T*)qn, (T*)qr, (T*)pages, T_););
     return q6k_check_launch("latent_prep");
 }
 

@@ -42,6 +42,7 @@ struct MmaArgs {
     int T_, H, Hkv;
     int nbuf;                           // 2: the next key tile is fetched (cp.async) while this one is used; 1: one buffer
     int v_heads;                        // > 0 (mixed heads): blockIdx.z is the value head and part_o is [T, H, v_heads, dv]
+    const float* sinks;                 // [H] or null: exp(sinks[h]) joins head h's softmax denominator (with split keys, in the merge)
 };
 
 __device__ __forceinline__ int first_visible_mma(int pos, int window, int chunk) {
@@ -356,7 +357,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
                     if (d < a.dv) *reinterpret_cast<float2*>(a.part_o + prow * a.dv + d) = make_float2(o[mb][nb][hf * 2], o[mb][nb][hf * 2 + 1]);
                 }
             } else {
-                const float inv = l_run[mb][hf] > 0.0f ? 1.0f / l_run[mb][hf] : 0.0f;
+                float l = l_run[mb][hf], corr = 1.0f;
+                if (a.sinks) {                                                   // the sink counts once in the denominator
+                    const float sk = a.sinks[h], mn = fmaxf(m_run[mb][hf], sk);
+                    corr = m_run[mb][hf] == -INFINITY ? 0.0f : expf(m_run[mb][hf] - mn);
+                    l = l * corr + expf(sk - mn);
+                }
+                const float inv = l > 0.0f ? corr / l : 0.0f;
                 const size_t orow = a.out_head_major ? (size_t)h * a.T_ + t : (size_t)t * a.H + h;
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
@@ -371,13 +378,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
 
 // Merges the key ranges of one (token, head) in order: out = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s.
 __global__ void __launch_bounds__(128) attention_flex_merge_kernel(const float* part_o, const float* part_ml, int nsplit, int T_, int H, int dv,
-                                                                   __nv_bfloat16* out, int out_head_major) {
+                                                                   __nv_bfloat16* out, int out_head_major, const float* sinks) {
     pdl_enter();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t row = (size_t)t * H + h, stride = (size_t)T_ * H;
-    float M = -INFINITY;
+    float M = sinks ? sinks[h] : -INFINITY;
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(s * stride + row) * 2]);
-    float L = 0.0f;
+    float L = sinks ? expf(sinks[h] - M) : 0.0f;
     for (int s = 0; s < nsplit; ++s) {
         const float m = part_ml[(s * stride + row) * 2];
         if (m != -INFINITY) L += expf(m - M) * part_ml[(s * stride + row) * 2 + 1];
@@ -438,7 +445,7 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
                                    const int* block_table, int max_blocks, int page_size, const int* req_of_token, const int* positions,
                                    const int* tile_tok0, const int* tile_ntok, int n_tiles, int window, int chunk, float scale, void* out,
                                    int out_head_major, int T_, int H, int Hkv, int nsplit, int split_keys, float* workspace,
-                                   const float* talk, cudaStream_t st) {
+                                   const float* talk, const float* sinks, cudaStream_t st) {
     if (T_ == 0 || n_tiles == 0) return 0;
     const int dk = da + db;
     const bool shared_v = v_pages == k_pages && v_ld == k_ld && v_head_stride == k_head_stride;
@@ -446,12 +453,12 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
     Q6K_REQUIRE((da == 0 || qa) && (db == 0 || qb) && nsplit >= 1 && (nsplit == 1 || (workspace && split_keys > 0 && split_keys % KEYS == 0)),
                 "attention_flex_mma: bad query parts or key split");
     Q6K_REQUIRE(Hkv <= 65535 && nsplit <= 65535, "attention_flex_mma: grid too large");
-    Q6K_REQUIRE(!talk || (nsplit == 1 && workspace && !out_head_major), "attention_flex_mma: mixed heads take one key range, scratch and token-major output");
+    Q6K_REQUIRE(!talk || (nsplit == 1 && workspace && !out_head_major && !sinks), "attention_flex_mma: mixed heads take one key range, scratch, token-major output and no sinks");
     MmaArgs a{qa, da, (const __nv_bfloat16*)qb, db, q_head_major, (const __nv_bfloat16*)k_pages, k_head_stride, k_ld,
               (const __nv_bfloat16*)v_pages, v_head_stride, v_ld, dv, block_table, max_blocks, page_size, req_of_token, positions,
               tile_tok0, tile_ntok, window, chunk, scale, (__nv_bfloat16*)out, out_head_major,
               workspace, workspace ? workspace + (size_t)nsplit * T_ * H * dv : nullptr, split_keys, nsplit, T_, H, Hkv,
-              flex_mma_smem(dk, dv, shared_v, 2) <= 220 * 1024 ? 2 : 1, talk ? Hkv : 0};
+              flex_mma_smem(dk, dv, shared_v, 2) <= 220 * 1024 ? 2 : 1, talk ? Hkv : 0, sinks};
     const size_t smem = flex_mma_smem(dk, dv, shared_v, a.nbuf);
     const int nb = ((dv + 7) / 8 + WARPS - 1) / WARPS;
     dim3 grid(n_tiles, Hkv, talk ? Hkv : nsplit);
@@ -472,7 +479,7 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
     }
     if (nsplit > 1) {
         q6k_launch(attention_flex_merge_kernel, dim3(T_, H), 128, 0, st, (const float*)a.part_o, (const float*)a.part_ml, nsplit, T_, H, dv,
-                   (__nv_bfloat16*)out, out_head_major);
+                   (__nv_bfloat16*)out, out_head_major, sinks);
         return q6k_check_launch("attention_flex_merge");
     }
     return 0;

@@ -65,6 +65,18 @@ __device__ __forceinline__ float q6k_activation(float z, int act) {
     return p * p;
 }
 
+// The gated epilogue's value for a gate product g and an up product u.  Codes 0 to 2: act(g) * u.  Code 3, the clamped
+// gate with its limit L (the launchers' `act_param`): g' = min(g, L), u' = clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1).
+constexpr int Q6K_ACT_CLAMPED = 3;
+__device__ __forceinline__ float q6k_gated(float g, float u, int act, float limit) {
+    if (act == Q6K_ACT_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return q6k_activation(g, act) * u;
+}
+
 // Programmatic dependent launch (the reference launches every Flint kernel this way,
 // crates/cuda/kernels/common.cuh:82-99).  A launch that carries the attribute may begin as soon as
 // every block of the kernel before it has executed pdl_launch() (or ended); it must execute

@@ -22,7 +22,7 @@ template <typename T, int EPI>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* A, int lda, const int* a_rows, const T* W, const T* W2,
                                                         size_t w_group_stride, void* out_, int ldo, int M, int N, int K,
                                                         const int* tile_group, const int* tile_row0,
-                                                        const int* group_offsets, const int* num_tiles, int act) {
+                                                        const int* group_offsets, const int* num_tiles, int act, float act_limit) {
     pdl_enter();
     constexpr bool DUAL = EPI == EPI_SWIGLU;
     __shared__ float As[BK][BM + 4];
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* A, int lda, con
                 ((T*)out_)[o] = from_f32<T>(q6k_activation(acc[i][j], act));
             } else {
                 const float gte = acc[i][j];
-                ((T*)out_)[o] = from_f32<T>((act == 0 ? gte / (1.0f + expf(-gte)) : q6k_activation(gte, act)) * acc2[DUAL ? i : 0][j]);
+                ((T*)out_)[o] = from_f32<T>(act == 0 ? gte / (1.0f + expf(-gte)) * acc2[DUAL ? i : 0][j] : q6k_gated(gte, acc2[DUAL ? i : 0][j], act, act_limit));
             }
         }
     }
@@ -158,13 +158,14 @@ Q6K_API int q6k_tile_list(const int* offsets, int G, int bm, int* tile_group, in
 // than there are groups); otherwise one group of M rows.
 Q6K_API int q6k_gemm_simt(const void* A, int lda, const int* a_rows, const void* W, const void* W2, long long w_group_stride,
                           void* out, int ldo, int M, int N, int K, const int* tile_group, const int* tile_row0,
-                          const int* group_offsets, const int* num_tiles, int max_tiles, int epilogue, int dtype,
+                          const int* group_offsets, const int* num_tiles, int max_tiles, int epilogue, float act_param, int dtype,
                           cudaStream_t st) {
     if (M == 0 || N == 0) return 0;
     Q6K_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
     const int act = epilogue >> 8;
     epilogue &= 255;
-    Q6K_REQUIRE(((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_ACT) && act >= 0 && act <= 2, "gemm: unknown epilogue %d (activation %d)", epilogue, act);
+    Q6K_REQUIRE(((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_ACT) && act >= 0 && act <= (epilogue == EPI_SWIGLU ? 3 : 2),
+                "gemm: unknown epilogue %d (activation %d)", epilogue, act);
     Q6K_REQUIRE(epilogue != EPI_SWIGLU || W2, "gemm: the SwiGLU epilogue needs two weight matrices");
     const int ytiles = tile_group ? max_tiles : (M + BM - 1) / BM;
     Q6K_REQUIRE(ytiles <= 65535, "gemm: %d row tiles exceed the grid limit", ytiles);
@@ -172,7 +173,7 @@ Q6K_API int q6k_gemm_simt(const void* A, int lda, const int* a_rows, const void*
 #define LAUNCH(EPI)                                                                                                     \
     q6k_launch(gemm_simt_kernel<T, EPI>, grid, 256, 0, st, (const T*)A, lda, a_rows, (const T*)W, (const T*)W2,                 \
                                                    (size_t)w_group_stride, out, ldo, M, N, K, tile_group, tile_row0, \
-                                                   group_offsets, num_tiles, act)
+                                                   group_offsets, num_tiles, act, act_param)
     Q6K_DISPATCH(dtype, {
         if (epilogue == EPI_STORE) LAUNCH(EPI_STORE);
         else if (epilogue == EPI_ADD) LAUNCH(EPI_ADD);

@@ -52,7 +52,8 @@ struct Params {
     unsigned* tickets;                 // pair mode with K slices: one arrival counter per (pair, n-tile), zero between launches
     int rows_total, N, K, ldo;
     int epilogue, stages, kb_per_split;
-    int act;                           // the activation of EPI_SWIGLU's gate and of EPI_ACT (q6k_activation's code)
+    int act;                           // the activation of EPI_SWIGLU's gate and of EPI_ACT (q6k_activation's code; 3: the clamped gate)
+    float act_limit;                   // the clamped gate's limit
     int pair_div;                      // > 0: one tile per (token, slot) pair, see q6k_gemm_tc_pairs
     int lists_old;                     // the pair list was written before the kernel launched before this one started: weights may be fetched before the wait
     int n_y, n_z;                      // row tiles (or pairs; an upper bound when num_tiles is given) and K slices
@@ -333,7 +334,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                         if (DUAL) b += __ldcg(mine + z * slice + p.N + n);
                     }
                     const size_t row = (size_t)tl.out0;
-                    if (p.epilogue == EPI_SWIGLU) ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn((p.act == 0 ? a / (1.0f + expf(-a)) : q6k_activation(a, p.act)) * b);
+                    if (p.epilogue == EPI_SWIGLU) ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(p.act == 0 ? a / (1.0f + expf(-a)) * b : q6k_gated(a, b, p.act, p.act_limit));
                     else if (p.epilogue == EPI_ACT) ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(q6k_activation(a, p.act));
                     else ((float*)p.out)[row * p.ldo + n] = a;
                 }
@@ -363,7 +364,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                             ((float*)p.out)[row * p.ldo + n] += v[j];
                         } else if (p.epilogue == EPI_SWIGLU) {
                             const float gte = v[j];
-                            ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn((p.act == 0 ? gte / (1.0f + expf(-gte)) : q6k_activation(gte, p.act)) * u[DUAL ? j : 0]);
+                            ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(p.act == 0 ? gte / (1.0f + expf(-gte)) * u[DUAL ? j : 0] : q6k_gated(gte, u[DUAL ? j : 0], p.act, p.act_limit));
                         } else if (p.epilogue == EPI_ACT) {
                             ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(q6k_activation(v[j], p.act));
                         } else {
@@ -771,7 +772,7 @@ Q6K_API long long q6k_gemm_tc_workspace(int rows, int N, int K) {
 // products stay in the workspace as FP32 [q6k_gemm_tc_splits, rows, N] for the caller's next
 // kernel to sum (in slice order) and `out` is not written.
 Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void* W, const void* W2, int groups, int N, int K,
-                        void* out, int ldo, int epilogue, const int* tile_group, const int* tile_row0,
+                        void* out, int ldo, int epilogue, float act_param, const int* tile_group, const int* tile_row0,
                         const int* group_offsets, const int* num_tiles, int max_tiles, int bt, float* workspace,
                         long long workspace_bytes, int keep_partials, cudaStream_t st) {
     if (rows_total == 0 || N == 0) return 0;
@@ -781,7 +782,8 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
                 "gemm_tc: operands must be 16-byte aligned");
     const int act = epilogue >> 8;
     epilogue &= 255;
-    Q6K_REQUIRE(((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_ACT) && act >= 0 && act <= 2, "gemm_tc: unknown epilogue %d (activation %d)", epilogue, act);
+    Q6K_REQUIRE(((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_ACT) && act >= 0 && act <= (epilogue == EPI_SWIGLU ? 3 : 2),
+                "gemm_tc: unknown epilogue %d (activation %d)", epilogue, act);
     Q6K_REQUIRE(epilogue != EPI_ACT || tile_group != nullptr, "gemm_tc: the activation of a single product is for grouped rows");
     const bool dual = epilogue == EPI_SWIGLU;
     Q6K_REQUIRE(!dual || W2, "gemm_tc: the SwiGLU epilogue needs two weight matrices");
@@ -809,7 +811,7 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     Params p{};
     p.out = out;
     p.tile_group = tile_group, p.tile_row0 = tile_row0, p.group_offsets = group_offsets, p.num_tiles = num_tiles;
-    p.rows_total = rows_total, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue, p.act = act;
+    p.rows_total = rows_total, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue, p.act = act, p.act_limit = act_param;
     // one row tile (dense), or groups of about one row tile each (experts with a prompt portion's rows): every
     // weight tile is fetched once, or by the few row tiles of its group, which lie side by side
     p.w_once = grouped ? (long long)rows_total <= 2LL * groups * bt : rows_total <= 128;
@@ -876,7 +878,7 @@ Q6K_API int q6k_gemm_tc_pairs_scratch(int pairs, int N, int K, int dual, long lo
 }
 
 Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const void* W, const void* W2, int groups, int N, int K,
-                              void* out, int ldo, int epilogue, const int* pair_expert, const int* pair_order, int pairs, int pair_div,
+                              void* out, int ldo, int epilogue, float act_param, const int* pair_expert, const int* pair_order, int pairs, int pair_div,
                               float* partial, long long partial_floats, unsigned* tickets, int n_tickets, int lists_old, cudaStream_t st) {
     if (pairs == 0 || N == 0) return 0;
     Q6K_REQUIRE(a_rows > 0 && N > 0 && K > 0 && groups > 0 && pairs > 0 && pair_div > 0, "gemm_tc_pairs: bad sizes rows=%d N=%d K=%d pairs=%d", a_rows, N, K, pairs);
@@ -884,7 +886,8 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
     Q6K_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && (!W2 || ((uintptr_t)W2 & 15) == 0), "gemm_tc_pairs: operands must be 16-byte aligned");
     const int act = epilogue >> 8;
     epilogue &= 255;
-    Q6K_REQUIRE((epilogue == EPI_STORE || epilogue == EPI_SWIGLU || epilogue == EPI_ACT) && act >= 0 && act <= 2, "gemm_tc_pairs: unknown epilogue %d (activation %d)", epilogue, act);
+    Q6K_REQUIRE((epilogue == EPI_STORE || epilogue == EPI_SWIGLU || epilogue == EPI_ACT) && act >= 0 && act <= (epilogue == EPI_SWIGLU ? 3 : 2),
+                "gemm_tc_pairs: unknown epilogue %d (activation %d)", epilogue, act);
     const bool dual = epilogue == EPI_SWIGLU;
     Q6K_REQUIRE(!dual || W2, "gemm_tc_pairs: the SwiGLU epilogue needs two weight matrices");
     Q6K_REQUIRE((long long)groups * N < (1LL << 31), "gemm_tc_pairs: too many weight rows");
@@ -895,7 +898,7 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
         if (int rc = weight_map(&tw2, W2, (long long)groups * N, K)) return rc;
     if (int rc = make_map(&ta, A, a_rows, K, lda, 16, false)) return rc;
     Params p{};
-    p.out = out, p.tile_group = pair_expert, p.rows_total = a_rows, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue, p.act = act;
+    p.out = out, p.tile_group = pair_expert, p.rows_total = a_rows, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue, p.act = act, p.act_limit = act_param;
     const int kb = (K + BK - 1) / BK;
     int splits = pair_splits(pairs, N, K);
     if (splits > 1) {

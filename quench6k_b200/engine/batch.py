@@ -48,6 +48,7 @@ class StepContext:
     hold_results: bool = False                    # a block that keeps a sublayer's result while other kernels run sets it: results
                                                   # must then be tensors of their own, not views of the products' scratch buffer
     position: int = 0                             # the executed position (index into the model's order) whose block is running
+    side_rows: Optional[torch.Tensor] = None      # FP32 [T, columns]: the tokens' rows of the model's side table, if it has one
 
     def query_tiles(self, tokens_per_tile: int, at_most: Optional[int] = None):
         """Tiles of at most `tokens_per_tile` consecutive tokens of one request, as device arrays

@@ -35,7 +35,10 @@ class DecoderModel:
                 after["norm1b"] = make_part(NORMS, "norm", ls.post_norm, size=D)
                 if ffn is not None:
                     after["norm2b"] = make_part(NORMS, "norm", ls.post_norm, size=D)
+            if ls.side is not None:
+                after["side"] = make_part(FEED_FORWARDS, "feed-forward", ls.side, hidden_size=D)
             self.blocks.append(BLOCKS[ls.block](norm1, mixer, norm2, ffn, **after, **ls.block_params))
+        self.embed_norm = make_part(NORMS, "norm", spec.embed_norm, size=D) if spec.embed_norm is not None else None
         self.final_norm = make_part(NORMS, "norm", spec.final_norm, size=D)
         self.order = list(spec.order)
         self.kv_source = list(spec.kv_source)
@@ -50,6 +53,10 @@ class DecoderModel:
     def tensors(self) -> List[TensorSpec]:
         s = self.spec
         out = [TensorSpec(s.embed_name, (s.vocab_size, s.hidden_size))]
+        if self.embed_norm is not None:
+            out += [TensorSpec(s.embed_norm_prefix + t.name, t.shape, t.role, t.init) for t in self.embed_norm.tensors()]
+        if s.side_table is not None:
+            out.append(TensorSpec(s.side_table[0], (s.vocab_size, s.side_table[1])))
         for ls, b in zip(s.layers, self.blocks):
             for sub, part in b.parts():
                 out += [TensorSpec(ls.prefix + s.sub_names[sub] + t.name, t.shape, t.role, t.init) for t in part.tensors()]
@@ -71,7 +78,7 @@ class DecoderModel:
         return [self.blocks[i].mixer.state_shape() for i in self.order]
 
     def graph_safe(self) -> bool:
-        parts = [self.final_norm]
+        parts = [self.final_norm] + ([self.embed_norm] if self.embed_norm is not None else [])
         for b in self.blocks:
             parts += [part for _, part in b.parts()]
         return all(getattr(x, "graph_safe", False) for x in parts)
@@ -81,6 +88,9 @@ class DecoderModel:
         s = self.spec
         self.rt = rt
         self.embed = to_operand(get(s.embed_name), rt)
+        if self.embed_norm is not None:
+            self.embed_norm.bind(lambda n: get(s.embed_norm_prefix + n), rt)
+        self.side_table = to_operand(get(s.side_table[0]), rt) if s.side_table is not None else None
         for ls, b in zip(s.layers, self.blocks):
             for sub, part in b.parts():
                 pre = ls.prefix + s.sub_names[sub]
@@ -94,6 +104,12 @@ class DecoderModel:
         [len(ctx.logit_rows), vocab] or None when no row is wanted."""
         ops.current_tag = "embedding"
         h = ops.embed(ctx.token_ids, self.embed, fed=ctx.fed)
+        if self.embed_norm is not None:
+            ops.current_tag = "norm.embedding"
+            self.embed_norm.normalize(h)
+        if self.side_table is not None:
+            ops.current_tag = "embedding.side"
+            ctx.side_rows = ops.embed(ctx.token_ids, self.side_table, fed=ctx.fed)
         h0 = h.clone() if self.readd else None      # the embedding output, for the passes of a repeated span that take it again
         pending = None                      # an add into h that a block has left to the next norm
         for p, i in enumerate(self.order):

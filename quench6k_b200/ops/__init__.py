@@ -217,15 +217,32 @@ def swiglu(gu: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
 # --------------------------------------------------------------------------- matrix products (CUDA cores)
 EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_ACT = 0, 1, 2, 4
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+# A gate that takes a constant is named with it, ("clamped", limit): with g the gate's product and u the other one,
+# g' = min(g, limit), u' = clamp(u, -limit, limit), and the result is g' sigmoid(1.702 g') (u' + 1).  Gated epilogues only.
+GATES_WITH_LIMIT = {"clamped": 3}
 
 
-def _epilogue(w2, accumulate: bool, act: Optional[str]) -> int:
+def act_has_param(act) -> bool:
+    return isinstance(act, tuple)
+
+
+def _act_code(act, gated: bool):
+    """(code, parameter) of an activation name or a (name, constant) pair."""
+    if isinstance(act, tuple):
+        name, param = act
+        if name not in GATES_WITH_LIMIT or not gated:
+            raise KernelError(f"unknown activation {act!r} (with a constant, for gated products: {', '.join(GATES_WITH_LIMIT)})")
+        return GATES_WITH_LIMIT[name], float(param)
+    if act not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {act!r}; known: {', '.join(ACTIVATIONS)}")
+    return ACTIVATIONS[act], 0.0
+
+
+def _epilogue(w2, accumulate: bool, act) -> int:
     """The launchers' epilogue argument: with w2 the gated epilogue act(x w^T) * (x w2^T) (SwiGLU when act is None or
     "silu"); with act alone act(x w^T), stored in the operand dtype; else store or add in FP32.  The activation's code
-    rides above bit 8."""
-    if act is not None and act not in ACTIVATIONS:
-        raise KernelError(f"unknown activation {act!r}; known: {', '.join(ACTIVATIONS)}")
-    code = ACTIVATIONS[act] << 8 if act is not None else 0
+    rides above bit 8 (its constant, if it has one, is `_act_param(act)`)."""
+    code = _act_code(act, w2 is not None)[0] << 8 if act is not None else 0
     if w2 is not None:
         return EPI_SWIGLU | code
     if act is not None:
@@ -233,6 +250,10 @@ def _epilogue(w2, accumulate: bool, act: Optional[str]) -> int:
             raise KernelError("an activated product is stored, not added")
         return EPI_ACT | code
     return EPI_ADD if accumulate else EPI_STORE
+
+
+def _act_param(act) -> float:
+    return float(act[1]) if isinstance(act, tuple) else 0.0
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
@@ -276,7 +297,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         offsets = tile_group = tile_row0 = num_tiles = None
         max_tiles = 0
     _call("q6k_gemm_simt", _ptr(a), _i(a.stride(0)), _ptr(a_rows), _ptr(w), _ptr(w2), _ll(stride), _ptr(out), _i(out.stride(0)),
-          _i(M), _i(N), _i(K), _ptr(tile_group), _ptr(tile_row0), _ptr(offsets), _ptr(num_tiles), _i(max_tiles), _i(epi),
+          _i(M), _i(N), _i(K), _ptr(tile_group), _ptr(tile_row0), _ptr(offsets), _ptr(num_tiles), _i(max_tiles), _i(epi), _f(_act_param(act)),
           _i(dtype_code(a.dtype)), _stream())
     return out
 
@@ -410,7 +431,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
                 ws = _workspace(ws_bytes, a.device)
                 ws_bytes = ws.numel() * 4
     _call("q6k_gemm_tc", _ptr(a), _ll(a.stride(0)), _i(M), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out), _i(out.stride(0)),
-          _i(epi), _ptr(tile_group), _ptr(tile_row0), _ptr(offsets), _ptr(num_tiles), _i(max_tiles), _i(bt), _ptr(ws),
+          _i(epi), _f(_act_param(act)), _ptr(tile_group), _ptr(tile_row0), _ptr(offsets), _ptr(num_tiles), _i(max_tiles), _i(bt), _ptr(ws),
           _ll(ws_bytes), _i(1 if keep_partials else 0), _stream())
     if keep_partials:
         return ws[: splits * M * N].view(splits, M, N)
@@ -861,7 +882,7 @@ def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, p
             tickets = torch.zeros(max(counters.value, 1024), dtype=torch.int32, device=a.device)
             _pair_scratch[key] = (partial, tickets)
     _call("q6k_gemm_tc_pairs", _ptr(a), _ll(a.stride(0)), _i(a.shape[0]), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out),
-          _i(out.stride(0)), _i(_epilogue(w2, False, act)), _ptr(pair_expert), _ptr(order), _i(pairs), _i(pair_div),
+          _i(out.stride(0)), _i(_epilogue(w2, False, act)), _f(_act_param(act)), _ptr(pair_expert), _ptr(order), _i(pairs), _i(pair_div),
           _ptr(partial), _ll(partial.numel() if partial is not None else 0), _ptr(tickets),
           _i(tickets.numel() if tickets is not None else 0), _i(1 if pairs_are_old else 0), _stream())
     return out
@@ -1125,22 +1146,25 @@ def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_
     return q
 
 
-def latent_prep(x: torch.Tensor, H: int, dim: int, rd: int, rank: int, c_weight: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor],
-                turn: int, positions: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
-                pages: torch.Tensor):
+def latent_prep(x: torch.Tensor, H: int, dim: int, rd: int, rank: int, c_weight: Optional[torch.Tensor], eps: float,
+                inv_freq: Optional[torch.Tensor], turn: int, positions: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor,
+                page_size: int, pages: torch.Tensor, neighbours: bool = False, write: bool = True):
     """x FP32 [T, H (dim + rd) + rank + rd] -> (qn [H, T, dim], qr [H, T, rd]) in the pages' dtype, and the token's row
-    [RMS-normed latent | rotated shared key part] into pages [1, P, page, rank + rd]."""
+    [RMS-normed latent | rotated shared key part] into pages [1, P, page, rank + rd].  neighbours: the rotation pairs
+    dimension 2i with 2i+1 instead of i with i + turn/2.  write=False: a layer that reads another layer's pages; x then
+    holds the queries only and nothing is written."""
     _need(x, "x", torch.float32)
     T = x.shape[0]
-    if x.shape[1] < H * (dim + rd) + rank + rd or tuple(pages.shape[2:]) != (page_size, rank + rd) or pages.shape[0] != 1:
+    if x.shape[1] < H * (dim + rd) + (rank + rd if write else 0) or tuple(pages.shape[2:]) != (page_size, rank + rd) or pages.shape[0] != 1:
         raise KernelError("latent_prep: shapes disagree")
     _need(pages, "pages")
-    _need(c_weight, "c_weight", torch.float32, (rank,))
+    if write:
+        _need(c_weight, "c_weight", torch.float32, (rank,))
     qn = torch.empty((H, T, dim), dtype=pages.dtype, device=x.device)
     qr = torch.empty((H, T, rd), dtype=pages.dtype, device=x.device)
-    _call("q6k_latent_prep", _ptr(x), _i(x.stride(0)), _i(T), _i(H), _i(dim), _i(rd), _i(rank), _ptr(c_weight), _f(eps), _ptr(inv_freq),
-          _i(turn), _ptr(positions), _ptr(req_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _ptr(qn), _ptr(qr),
-          _ptr(pages), _i(dtype_code(pages.dtype)), _stream())
+    _call("q6k_latent_prep", _ptr(x), _i(x.stride(0)), _i(T), _i(H), _i(dim), _i(rd), _i(rank), _ptr(c_weight if write else None), _f(eps),
+          _ptr(inv_freq), _i(turn), _i(1 if neighbours else 0), _ptr(positions), _ptr(req_of_token), _ptr(block_table), _i(block_table.shape[1]),
+          _i(page_size), _ptr(qn), _ptr(qr), _ptr(pages if write else None), _i(dtype_code(pages.dtype)), _stream())
     return qn, qr
 
 
@@ -1156,13 +1180,14 @@ def heads_to_rows(src: torch.Tensor, H: int, out_dtype: torch.dtype) -> torch.Te
 def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], head_major: bool, k_pages: torch.Tensor, v_pages: torch.Tensor,
                    block_table: torch.Tensor, req_of_token: torch.Tensor, positions: torch.Tensor, H: int, scale: float,
                    window: Optional[int] = None, chunk: Optional[int] = None, talk: Optional[torch.Tensor] = None,
-                   out_head_major: bool = False, tiles=None, max_context: int = 0) -> torch.Tensor:
+                   out_head_major: bool = False, tiles=None, max_context: int = 0, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every row over its request's pages, for any key and value widths.  A query row is the FP32
     part q_f32 [H*T or T*H rows, da] followed by q [rows, db] in the pages' dtype (either may be None); rows are head-major
     (h T + t) or token-major.  k_pages [Hkv, P, page, dk]; v_pages [Hkv, P, page, dv], possibly a view into k_pages (the
     last axis contiguous, the others with k's strides).  window: only the last `window` keys; chunk: only keys of the
     position's own block of `chunk` positions; talk FP32 [H, H]: the heads' softmax weights are mixed by it before the
-    values.  Returns [H, T, dv] (out_head_major) or [T, H dv].
+    values; sinks FP32 [H]: exp(sinks[h]) joins head h's softmax denominator (it has no key and no value, is not scaled
+    and counts once).  Returns [H, T, dv] (out_head_major) or [T, H dv].
     tiles = (first row, token count, number) of row tiles of attention_flex_tile_tokens(H, Hkv) tokens of one request
     each, with max_context the largest position + 1 of the step: bfloat16 pages then go to the tensor-core kernel where
     it takes the shapes; with few tiles it splits the keys into fixed ranges and merges them."""
@@ -1183,6 +1208,8 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
             raise KernelError(f"attention_flex: {nm} has strides {p.stride()}")
     if talk is not None:
         _need(talk, "talk", torch.float32, (H, H))
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (H,))
     out = torch.empty((H, T, dv) if out_head_major else (T, H * dv), dtype=k_pages.dtype, device=k_pages.device)
     shared_v = v_pages.data_ptr() == k_pages.data_ptr() and v_pages.stride() == k_pages.stride()
     if (tiles is not None and k_pages.dtype == torch.bfloat16 and not (talk is not None and out_head_major)
@@ -1206,12 +1233,12 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
               _ll(k_pages.stride(0)), _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv),
               _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tok0), _ptr(ntok),
               _i(n_tiles), _i(window or 0), _i(chunk or 0), _f(scale), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv),
-              _i(nsplit), _i(split_keys), _ptr(ws), _ptr(talk), _stream())
+              _i(nsplit), _i(split_keys), _ptr(ws), _ptr(talk), _ptr(sinks), _stream())
         return out
     _call("q6k_attention_flex", _ptr(q_f32), _i(da), _ptr(q), _i(db), _i(1 if head_major else 0), _ptr(k_pages), _ll(k_pages.stride(0)),
           _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _i(chunk or 0), _f(scale),
-          _ptr(talk), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv), _i(dtype_code(k_pages.dtype)), _stream())
+          _ptr(talk), _ptr(sinks), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv), _i(dtype_code(k_pages.dtype)), _stream())
     return out
 
 
@@ -1377,3 +1404,87 @@ def route_biased(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], sca
     sel_w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
     _call("q6k_route_biased", _ptr(logits), _i(slices), _ptr(bias), _f(scale), _i(T), _i(E), _i(k), _ptr(sel_e), _ptr(sel_w), _stream())
     return sel_e, sel_w
+
+
+# --------------------------------------------------------------------------- sublayers whose results pass a norm before the stream
+def add_normed(h: torch.Tensor, y: Optional[torch.Tensor], w: Optional[torch.Tensor], eps: float, out_dtype: Optional[torch.dtype] = None,
+               weighted=None) -> Optional[torch.Tensor]:
+    """h += (y + weighted rows) / rms(y + weighted rows) * w in place on the FP32 stream h [T, D]; y FP32 [T, D] or
+    [slices, T, D] partial sums added in order (or None), weighted = (rows [pairs, D], pair_row [T, S] or None, weights
+    [T, S]) as in `combine` (or None).  With neither, nothing is added.  out_dtype: also return the stream as it then
+    stands in that dtype (what the next sublayer reads)."""
+    _need(h, "h", torch.float32)
+    T, D = h.shape
+    slices, stride = 1, 0
+    if y is not None:
+        _need(y, "y", torch.float32)
+        slices, stride, rows, cols = _slices_of(y)
+        if (rows, cols) != (T, D):
+            raise KernelError("add_normed: the sublayer's result does not match the stream")
+    py = pair_row = pw = None
+    S = 0
+    if weighted is not None:
+        py, pair_row, pw = weighted
+        _need(py, "weighted rows", torch.float32)
+        _need(pw, "weights", torch.float32)
+        S = pw.shape[1]
+        if pair_row is not None:
+            _need(pair_row, "pair_row", torch.int32)
+        if pw.shape[0] != T or py.shape[1] != D or py.shape[0] < T * S or (pair_row is not None and pair_row.numel() != T * S):
+            raise KernelError("add_normed: the weighted rows do not match the stream")
+    if y is None and weighted is None and out_dtype is None:
+        return None
+    if y is not None or weighted is not None:
+        _need(w, "w", torch.float32, (D,))
+    out = torch.empty((T, D), dtype=out_dtype, device=h.device) if out_dtype is not None else None
+    _call("q6k_add_normed", _ptr(h), _ptr(y), _i(slices), _ll(stride), _ptr(py), _ptr(pair_row), _ptr(pw), _i(S), _ptr(w), _f(eps), _ptr(out),
+          _i(T), _i(D), _i(dtype_code(out_dtype or torch.float32)), _stream())
+    return out
+
+
+def side_gate(p: torch.Tensor, e: torch.Tensor, col0: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """out_dtype(gelu_tanh(p[t, j]) * e[t, col0 + j]): p FP32 [T, n] (or [slices, T, n] partial sums), e FP32 [T, *]."""
+    _need(p, "p", torch.float32)
+    _need(e, "e", torch.float32)
+    slices, stride, T, n = _slices_of(p)
+    if e.shape[0] != T or col0 + n > e.shape[1]:
+        raise KernelError("side_gate: shapes disagree")
+    out = torch.empty((T, n), dtype=out_dtype, device=p.device)
+    _call("q6k_side_gate", _ptr(p), _i(slices), _ll(stride), _ptr(e), _i(e.stride(0)), _i(col0), _ptr(out), _i(T), _i(n), _i(dtype_code(out_dtype)),
+          _stream())
+    return out
+
+
+# --------------------------------------------------------------------------- retention
+@functools.lru_cache(maxsize=None)
+def retention_max_dim() -> int:
+    lib = library()
+    lib.q6k_retention_max_dim.restype = ctypes.c_int
+    return lib.q6k_retention_max_dim()
+
+
+def retention_prep(p: torch.Tensor, H: int, dk: int, q_col: int, k_col: int, rotary, k_scale: float, positions: torch.Tensor) -> None:
+    """In place on p FP32 [T, N]: the first rotary_dim entries of every head of q (columns q_col...) and k (k_col...)
+    turn by position * inv_freq[pair]; k is then multiplied by k_scale.  rotary = (inv_freq, rotary_dim, neighbours) or None."""
+    _need(p, "p", torch.float32)
+    inv_freq, rd, neighbours = rotary if rotary is not None else (None, 0, False)
+    if p.dim() != 2 or max(q_col, k_col) + H * dk > p.shape[1]:
+        raise KernelError("retention_prep: shapes disagree")
+    _call("q6k_retention_prep", _ptr(p), _i(p.stride(0)), _i(p.shape[0]), _i(H), _i(dk), _i(q_col), _i(k_col), _ptr(inv_freq), _i(rd),
+          _i(1 if neighbours else 0), _f(k_scale), _ptr(positions), _stream())
+
+
+def retention(p: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+              slot_ids: torch.Tensor, R: int, H: int, dk: int, dv: int, chunked: bool = False) -> torch.Tensor:
+    """Per request and head, in token order: S <- decay[h] S + k v^T, o = S^T q.  p FP32 [T, N] with q, k (prepared) and v
+    at their columns; state FP32 [slots, H, dv, dk], updated in place; returns o FP32 [T, H dv].  chunked: the kernel for
+    prompt portions, which takes a request's tokens a chunk at a time (the same sums, regrouped)."""
+    _need(p, "p", torch.float32)
+    _need(decay, "decay", torch.float32, (H,))
+    _need(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (H, dv, dk) or p.dim() != 2 or max(q_col, k_col) + H * dk > p.shape[1] or v_col + H * dv > p.shape[1]:
+        raise KernelError("retention: shapes disagree")
+    o = torch.empty((p.shape[0], H * dv), dtype=torch.float32, device=p.device)
+    _call("q6k_retention", _ptr(p), _i(p.stride(0)), _i(q_col), _i(k_col), _i(v_col), _ptr(decay), _ptr(state), _ptr(q_start), _ptr(slot_ids),
+          _i(R), _ptr(o), _i(H), _i(dk), _i(dv), _stream())
+    return o

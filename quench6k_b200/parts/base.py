@@ -109,11 +109,15 @@ class PostNormed:
     """A residual add that has not been made yet: h += norm(y), the closing step of a sublayer whose result passes a norm
     of its own before it joins the stream.  A block may return it instead of adding, and a norm that understands it
     (Norm.fuses_post_normed) makes the add in the pass that normalises for the next sublayer."""
-    y: torch.Tensor                       # FP32 [T, D], or [slices, T, D] partial sums to be added in order
+    y: Optional[torch.Tensor]             # FP32 [T, D], or [slices, T, D] partial sums to be added in order
     norm: "Norm"
+    weighted: Optional[WeightedRows] = None    # unsummed rows that join y before the norm (norms whose add_normed takes them)
 
     def apply(self, h: torch.Tensor) -> None:
-        self.norm.add_normed(h, self.y)
+        if self.weighted is not None:
+            self.norm.add_normed(h, self.y, weighted=self.weighted)
+        else:
+            self.norm.add_normed(h, self.y)
 
 
 @dataclass
@@ -161,6 +165,10 @@ class Norm(Part):
         """h += this norm of y (y FP32 [T, D] or [slices, T, D] partial sums), in place."""
         raise NotImplementedError
 
+    def normalize(self, h: torch.Tensor) -> None:
+        """h <- this norm of h, in place on the FP32 stream."""
+        raise NotImplementedError
+
     def forward(self, h: torch.Tensor, rows: Optional[torch.Tensor] = None, add=None) -> torch.Tensor:
         """Normalised rows of h in the operand dtype.  `add`: FP32 of h's shape, or [slices, T, D]
         partial sums, or (if fuses_weighted_rows) a WeightedRows: added into h first, in place."""
@@ -206,14 +214,15 @@ class Block:
     takes_extra = False                   # forward(..., extra=x) adds x into the stream inside the block's first norm
 
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward],
-                 norm1b: Optional[Norm] = None, norm2b: Optional[Norm] = None):
+                 norm1b: Optional[Norm] = None, norm2b: Optional[Norm] = None, side: Optional[FeedForward] = None):
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
         self.norm1b, self.norm2b = norm1b, norm2b      # norms of the sublayers' results, in arrangements that have them
+        self.side = side                               # a third sublayer fed by the model's side table, in arrangements that have one
 
     def parts(self):
         """(role, part) of everything that holds tensors, in the order the tensors are declared."""
         out = [("norm1", self.norm1), ("mixer", self.mixer), ("norm2", self.norm2), ("ffn", self.ffn),
-               ("norm1b", self.norm1b), ("norm2b", self.norm2b)]
+               ("norm1b", self.norm1b), ("norm2b", self.norm2b), ("side", self.side)]
         return [(k, v) for k, v in out if v is not None]
 
     def forward(self, h, ctx, cache, state, pending=None):

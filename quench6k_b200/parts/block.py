@@ -91,3 +91,41 @@ class ParallelBlock(Block):
         acc = h.new_zeros(h.shape)
         self.ffn.forward(x2, ctx, acc)
         return ScaledSum(self.scale, y, acc)
+
+
+@register_block("outnorm")
+class OutNormBlock(Block):
+    """A norm on each sublayer's result only: h += norm1(mixer(h)); h += norm2(ffn(h)); h += side.norm(side(h)), the
+    sublayers reading the stream itself (in the operand dtype).  A block may lack the feed-forward, the side sublayer or
+    both.  Each closing add is made by the kernel that also hands the stream to the next sublayer, one pass over the row;
+    the block's last add is left to the block after it (or to the model's last norm)."""
+
+    def _close(self, h, pending, dtype):
+        """Makes the add that is left and returns the stream as it then stands, in the operand dtype."""
+        if isinstance(pending, PostNormed) and isinstance(pending.norm, RMSNorm):
+            return pending.norm.add_normed(h, pending.y, weighted=pending.weighted, out_dtype=dtype)
+        if pending is not None:
+            pending.apply(h)
+        return ops.add_normed(h, None, None, 0.0, dtype)
+
+    def forward(self, h, ctx, cache, state, pending=None):
+        dtype = self.mixer.rt.dtype
+        ops.current_tag = "stream.mixer"
+        x = self._close(h, pending, dtype)
+        y = self.mixer.forward(x, ctx, cache, state, None)
+        if y is None:
+            raise TypeError(f"{type(self.mixer).__name__} adds into the stream itself; this arrangement needs its result")
+        left = PostNormed(y, self.norm1)
+        if self.ffn is not None:
+            ops.current_tag = "stream.ffn"
+            x = self._close(h, left, dtype)
+            if getattr(self.ffn, "defers_add", False):
+                y, rows = self.ffn.compute(x, ctx)            # (the part every token shares or None, the routed rows unsummed)
+                left = PostNormed(y, self.norm2, rows)
+            else:
+                left = PostNormed(self.ffn.compute(x, ctx), self.norm2)
+        if self.side is not None:
+            ops.current_tag = "stream.side"
+            x = self._close(h, left, dtype)
+            left = PostNormed(self.side.compute(x, ctx), self.side.norm)
+        return left

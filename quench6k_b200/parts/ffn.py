@@ -18,15 +18,24 @@ from . import linear
 from .base import FeedForward, WeightedRows, register_feed_forward, to_f32, to_operand
 
 
+def _checked_act(act):
+    if isinstance(act, (tuple, list)):
+        if len(act) != 2 or act[0] not in ops.GATES_WITH_LIMIT:
+            raise ValueError(f"unknown gate {act!r}; with a constant: {', '.join(ops.GATES_WITH_LIMIT)}")
+        return (act[0], float(act[1]))
+    if act not in ops.ACTIVATIONS:
+        raise ValueError(f"unknown activation {act!r}; known: {', '.join(ops.ACTIVATIONS)}")
+    return act
+
+
 @register_feed_forward("dense")
 class DenseSwiGLU(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, names=None, act: str = "silu"):
-        """act: what the gate passes through, one of ops.ACTIVATIONS (applied in the epilogue of the gate/up product)."""
-        if act not in ops.ACTIVATIONS:
-            raise ValueError(f"unknown activation {act!r}; known: {', '.join(ops.ACTIVATIONS)}")
-        self.D, self.I, self.act = hidden_size, intermediate_size, act
+        """act: what the gate passes through, one of ops.ACTIVATIONS, or a gate with its constant such as ("clamped", limit)
+        (ops.GATES_WITH_LIMIT); applied in the epilogue of the gate/up product."""
+        self.D, self.I, self.act = hidden_size, intermediate_size, _checked_act(act)
         # the tensors' names relative to the part's prefix (an architecture may call them anything)
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
 
@@ -61,12 +70,16 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int, scoring: str = "softmax",
                  renormalize: bool = True, shared_intermediate_size: int = 0, gated: bool = True, act: str = "silu",
-                 correction: bool = False, route_scale: float = 1.0, names=None):
+                 correction: bool = False, route_scale: float = 1.0, names=None, shared_act=None, shared_prefix: str = "shared_experts.",
+                 shared_names=None):
         """gated: an expert is down(act(gate x) * (up x)); else down(act(up x)).  correction: a stored vector added to the
         scores for the choice of the experts only (the weights use the scores without it); route_scale multiplies the
-        weights.  Both belong to sigmoid scoring with renormalised weights."""
-        if act not in ops.ACTIVATIONS:
-            raise ValueError(f"unknown activation {act!r}; known: {', '.join(ops.ACTIVATIONS)}")
+        weights.  Both belong to sigmoid scoring with renormalised weights.  act may be a gate with its constant, such as
+        ("clamped", limit) (gated experts only).  The shared expert has the experts' form with an activation (shared_act,
+        default the experts'), a tensor prefix and tensor names of its own."""
+        act = _checked_act(act)
+        if isinstance(act, tuple) and not gated:
+            raise ValueError(f"the gate {act[0]!r} belongs to gated experts")
         self.gated, self.act, self.has_correction, self.route_scale = bool(gated), act, bool(correction), float(route_scale)
         self.own_router = self.has_correction or self.route_scale != 1.0
         if self.own_router and not (scoring == "sigmoid" and renormalize):
@@ -79,7 +92,9 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"top_k {top_k} outside 1..{num_experts}")
         self.D, self.E, self.k, self.I = hidden_size, num_experts, top_k, intermediate_size
         self.scoring, self.renorm = scoring, bool(renormalize)
-        self.shared = DenseSwiGLU(hidden_size, shared_intermediate_size) if shared_intermediate_size > 0 else None
+        self.shared_prefix = shared_prefix
+        self.shared = (DenseSwiGLU(hidden_size, shared_intermediate_size, names=shared_names, act=shared_act if shared_act is not None else act)
+                       if shared_intermediate_size > 0 else None)
         self.always_defers = self.shared is None      # forward(defer=True) never touches `out`
         self.pair_tokens = 16                         # steps of at most this many tokens run the experts pair by pair
         self.routing_tap = None               # a parts.base.Tap: every forward records each row's chosen experts [T, k]
@@ -94,7 +109,7 @@ class RoutedExperts(FeedForward):
         if self.has_correction:
             out.append(TensorSpec(n["correction"], (E,), "f32", ("normal", 0.1)))
         if self.shared is not None:
-            out += [TensorSpec("shared_experts." + t.name, t.shape, t.role, t.init) for t in self.shared.tensors()]
+            out += [TensorSpec(self.shared_prefix + t.name, t.shape, t.role, t.init) for t in self.shared.tensors()]
         return out
 
     def bind(self, get, rt):
@@ -106,7 +121,7 @@ class RoutedExperts(FeedForward):
         self.w_down = to_operand(get(n["down"]), rt)
         self.correction = to_f32(get(n["correction"]), rt) if self.has_correction else None
         if self.shared is not None:
-            self.shared.bind(lambda n: get("shared_experts." + n), rt)
+            self.shared.bind(lambda n: get(self.shared_prefix + n), rt)
 
     defers_add = True
 
@@ -119,13 +134,19 @@ class RoutedExperts(FeedForward):
         self.routing_tap.record("experts", ctx.position, sel_e)
         self.routing_tap.record("router_logits", ctx.position, logits)
 
-    def forward(self, xn, ctx, out, defer=False):
+    def compute(self, xn, ctx):
+        """(the shared expert's result FP32 [T, D] or split-K slices of it, or None; the routed experts' results unsummed,
+        a WeightedRows): for a block whose norm takes the sum before the stream does."""
+        rows = self.forward(xn, ctx, None, defer=True, routed_only=True)
+        return (self.shared.compute(xn, ctx) if self.shared is not None else None), rows
+
+    def forward(self, xn, ctx, out, defer=False, routed_only=False):
         """Adds the experts' weighted results into `out`; with defer=True and no shared expert it
-        returns them unsummed (WeightedRows) for the next norm to add."""
+        returns them unsummed (WeightedRows) for the next norm to add.  routed_only: the shared expert is the caller's."""
         rt = self.rt
         T = xn.shape[0]
         pairs = T * self.k
-        defer = defer and self.shared is None
+        defer = defer and (self.shared is None or routed_only)
         if (self.gated and self.act == "silu" and not self.own_router and rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
                 and ops.tc_supported(xn, self.w_gate) and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per

@@ -29,6 +29,16 @@ class RMSNorm(Norm):
 
     fuses_weighted_rows = True
 
+    def add_normed(self, h, y, weighted=None, out_dtype=None):
+        """h += this norm of (y + weighted rows) in place (y FP32 [T, D] or [slices, T, D] partial sums, or None; weighted a
+        WeightedRows or None); with out_dtype also the stream as it then stands, in that dtype."""
+        w = None if weighted is None else (weighted.y, weighted.pair_row, weighted.weights)
+        return ops.add_normed(h, y, self.weight, self.eps, out_dtype, weighted=w)
+
+    def normalize(self, h):
+        """h <- this norm of h, in place on the FP32 stream."""
+        return ops.rmsnorm(h, self.weight, self.eps, h.dtype, out=h)
+
     def forward(self, h, rows=None, add=None):
         if isinstance(add, WeightedRows):
             return ops.rmsnorm(h, self.weight, self.eps, self.rt.dtype, rows=rows, weighted=(add.y, add.pair_row, add.weights))

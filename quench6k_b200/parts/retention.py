@@ -1,0 +1,84 @@
+"""A retention mixer: linear attention with one fixed decay per head and neither softmax nor denominator.  Per head a
+matrix-valued state S [dk, dv] starts at zero and is carried from token to token:
+
+    S <- decay_h S + k v^T;   o = S^T q
+
+q and k pass a rotation by position (over all or the leading part of a head) and k is then multiplied by a scale; each
+head's o is divided by its root mean square (no weight), multiplied by silu(W_g x), and leaves through the output product.
+
+The products run on the engine's matrix kernels (q, k, v and the gate as one stacked product); the rotation, the
+recurrence (csrc/retention.cu) and the output norm are kernels of their own and FP32 throughout.  Each request keeps S
+(FP32) in its state slot, so a prompt may be cut anywhere and a decoded token costs one step of the recurrence.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..spec import PartSpec, TensorSpec
+from . import linear
+from .base import POSITION_ENCODINGS, Mixer, make_part, register_mixer
+
+_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "gate": "g_proj.weight", "o": "o_proj.weight"}
+
+
+@register_mixer("retention")
+class Retention(Mixer):
+    graph_safe = True
+    chunk_beyond = 32            # steps whose longest portion has more tokens walk prompts a chunk at a time
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, v_dim: int, decay, eps: float, pos: PartSpec, k_scale=None, names=None):
+        """decay: one number per head.  k_scale: what k is multiplied by after the rotation (default head_dim^-1/2)."""
+        decay = [float(d) for d in decay]
+        if len(decay) != num_heads:
+            raise ValueError(f"{len(decay)} decays for {num_heads} heads")
+        self.D, self.H, self.dk, self.dv, self.decay, self.eps = hidden_size, num_heads, head_dim, v_dim, decay, float(eps)
+        self.k_scale = float(k_scale) if k_scale is not None else head_dim ** -0.5
+        self.pos = make_part(POSITION_ENCODINGS, "position encoding", pos)
+        if not self.pos.is_identity and self.pos.rotary_table is None:
+            raise ValueError("the retention kernels take a rotation of pairs or no position encoding")
+        self.names = {**_NAMES, **(names or {})}
+        # columns of the stacked product: [q | k | v | gate]
+        self.k_col, self.v_col, self.g_col = num_heads * head_dim, 2 * num_heads * head_dim, 2 * num_heads * head_dim + num_heads * v_dim
+        self.N = self.g_col + num_heads * v_dim
+
+    def tensors(self):
+        n, D, H, dk, dv = self.names, self.D, self.H, self.dk, self.dv
+        return [TensorSpec(n["q"], (H * dk, D)), TensorSpec(n["k"], (H * dk, D)), TensorSpec(n["v"], (H * dv, D)),
+                TensorSpec(n["gate"], (H * dv, D)), TensorSpec(n["o"], (D, H * dv))]
+
+    def bind(self, get, rt):
+        if self.dk > ops.retention_max_dim():
+            raise ValueError(f"keys of {self.dk} entries: the retention kernel takes up to {ops.retention_max_dim()}")
+        self.rt = rt
+        n = self.names
+        self.w_in = torch.empty((self.N, self.D), dtype=rt.dtype, device=rt.device)
+        at = 0
+        for name in ("q", "k", "v", "gate"):
+            w = get(n[name])
+            self.w_in[at:at + w.shape[0]].copy_(w)
+            at += w.shape[0]
+        self.w_o = torch.empty((self.D, self.H * self.dv), dtype=rt.dtype, device=rt.device)
+        self.w_o.copy_(get(n["o"]))
+        self.decay_t = torch.tensor(self.decay, dtype=torch.float32).to(rt.device)
+        self.ones = torch.ones(self.dv, dtype=torch.float32, device=rt.device)       # the output norm has no weight
+        self.pos.bind(lambda name: get("position." + name), rt)
+
+    def state_shape(self):
+        # the state is kept column-major: a column's rows lie together
+        return {"S": ((self.H, self.dv, self.dk), torch.float32)}
+
+    def forward(self, xn, ctx, cache, state, out):
+        rt = self.rt
+        ops.current_tag = "retention.in"
+        p = linear.matmul(xn, self.w_in, rt)                                      # FP32 [T, q | k | v | gate]
+        ops.current_tag = "retention.prepare"
+        ops.retention_prep(p, self.H, self.dk, 0, self.k_col, None if self.pos.is_identity else self.pos.rotary_table(), self.k_scale,
+                           ctx.positions)
+        ops.current_tag = "retention.recurrence"
+        o = ops.retention(p, 0, self.k_col, self.v_col, self.decay_t, state["S"], ctx.q_start, ctx.slot_ids, ctx.R, self.H, self.dk, self.dv,
+                          chunked=ctx.max_q_len > self.chunk_beyond)
+        ops.current_tag = "retention.out"
+        y = ops.delta_out(o, p, self.g_col, self.ones, self.eps, self.H, self.dv, rt.dtype)
+        ops.current_tag = "retention.o"
+        return linear.matmul(y, self.w_o, rt, partials_ok=not ctx.hold_results)

@@ -27,6 +27,7 @@ class LayerSpec:
     block: str = "prenorm"      # arrangement, a key of parts.BLOCKS
     post_norm: Optional[PartSpec] = None    # the kind of the norms on the sublayers' results, in arrangements that have them
     block_params: Dict[str, Any] = field(default_factory=dict)   # constants of the arrangement (a multiplier on what it adds, ...)
+    side: Optional[PartSpec] = None         # a third sublayer fed by the model's side table (arrangements that have one)
 
 
 @dataclass
@@ -46,10 +47,16 @@ class ModelSpec:
     ignorable: Optional[Callable[[str], bool]] = None    # stored tensors that may be there without being declared
     # what follows a layer's prefix for each of its parts (a part's own tensor names come after it)
     sub_names: Dict[str, str] = field(default_factory=lambda: {"norm1": "input_layernorm.", "mixer": "self_attn.",
-                                                                "norm2": "post_attention_layernorm.", "ffn": "mlp."})
+                                                                "norm2": "post_attention_layernorm.", "ffn": "mlp.",
+                                                                "side": "side."})
     # executed positions before which the embedding output is added to the stream again (a span of layers run several
     # times takes its input anew at the start of every pass but the first)
     readd_embedding: Tuple[int, ...] = ()
+    embed_norm: Optional[PartSpec] = None  # a norm applied to the embedding output before the first layer
+    embed_norm_prefix: str = "model.embed_norm."
+    # a second embedding table (name, columns): the step gathers the tokens' rows of it once, FP32, and layers read their
+    # columns of them (StepContext.side_rows)
+    side_table: Optional[Tuple[str, int]] = None
 
 
 @dataclass

@@ -341,8 +341,29 @@ def flint_routed_config(size):
             "sliding_window_pattern": [True] * 8}
 
 
+def sigusun_config(size):
+    """Sigusun at layer sizes that resemble a real model's: a retention layer, a latent attention layer in a sliding window, a
+    second one that reads the first one's cached latent, and a causal latent attention layer with sinks; every layer with
+    clamped routed experts, a shared expert and the per-layer token input; eight layers (the four kinds twice)."""
+    D, heads, rank, E, top, eff, window = {"s": (1024, 8, 256, 32, 4, 512, 1024), "m": (2048, 16, 512, 64, 4, 1024, 2048)}[size]
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": E, "top": top}, "shared": {"ff": eff, "limit": 7.0}}
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": rank, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    ret = {"type": "retention", "mlp": moe,
+           "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / heads) for h in range(heads)],
+                     "rot": {"base": 10000.0, "dims": 128}}}
+    win = {"type": "latent_attention", "mlp": moe, "mixer": dict(latent, mask={"size": window})}
+    sink = {"type": "latent_attention_2", "mlp": moe, "mixer": dict(latent)}
+    layers = []
+    for rep in range(2):
+        at = len(layers)
+        layers += [ret, win, dict(win, mixer=dict(win["mixer"], kv_from=at + 1)), sink]
+    return {"architecture": "Sigusun", "vocab": 32768, "width": D, "norm": {"eps": 1e-6}, "token_side": {"dim": 64}, "kv_page_size": 16,
+            "layers": layers}
+
+
 DESIGNS = {"pedotar": (("pedotar", pedotar_config), ("flint_dense", flint_dense_config)),
-           "kipedra": (("kipedra", kipedra_config), ("flint_routed", flint_routed_config))}
+           "kipedra": (("kipedra", kipedra_config), ("flint_routed", flint_routed_config)),
+           "sigusun": (("sigusun", sigusun_config), ("kipedra", kipedra_config), ("pedotar", pedotar_config))}
 
 
 def design_compare(args):
@@ -505,9 +526,9 @@ def main():
     ap.add_argument("--profile-ops", action="store_true",
                     help="instead of the benchmark line: where an eager decode step and a prefill step spend their time, launcher by "
                          "launcher (CUDA events around every launch; its own JSON line)")
-    ap.add_argument("--design", default=None, choices=["pedotar", "kipedra"],
+    ap.add_argument("--design", default=None, choices=["pedotar", "kipedra", "sigusun"],
                     help="instead of the benchmark line: prefill and decode throughput of that design beside the closest Flint model "
-                         "(pedotar: dense feed-forwards; kipedra: windows and routed experts) at equal layer sizes (--sizes), with each "
+                         "(pedotar: dense feed-forwards; kipedra: windows and routed experts; sigusun: beside Kipedra and Pedotar) at equal layer sizes (--sizes), with each "
                          "model's time launcher by launcher (its own JSON line)")
     ap.add_argument("--sizes", default="s,m", help="--design: s (width 1024) and/or m (width 2048)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gated_delta"],

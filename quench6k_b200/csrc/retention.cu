@@ -9,10 +9,6 @@
 //    column: lane l holds rows l, l + 32, ... of it in registers.  A token costs one fused multiply-add per element and
 //    one sum over the rows (lane-strided partial sums, then a butterfly: the same order for every token wherever a prompt
 //    was cut).  q, k and v of 16 tokens at a time are staged in shared memory.
-//  * retention_chunk_kernel does the same for prompt portions, 32 tokens at a time: with P the state before a chunk that
-//    starts at token a, o_t = decay^(t-a+1) P^T q_t + sum_(a <= s <= t) decay^(t-s) (q_t . k_s) v_s, and the state after it
-//    is decay^n P + sum_s decay^(a+n-1-s) k_s v_s^T.  Chunks are counted from the start of the request's portion, so
-//    cutting a prompt elsewhere regroups sums and changes results by rounding only.
 //
 // Everything is FP32: angles, the rotation, decays and their powers, the state and every sum.
 #include "common.cuh"

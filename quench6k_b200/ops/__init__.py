@@ -1475,10 +1475,9 @@ def retention_prep(p: torch.Tensor, H: int, dk: int, q_col: int, k_col: int, rot
 
 
 def retention(p: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
-              slot_ids: torch.Tensor, R: int, H: int, dk: int, dv: int, chunked: bool = False) -> torch.Tensor:
+              slot_ids: torch.Tensor, R: int, H: int, dk: int, dv: int) -> torch.Tensor:
     """Per request and head, in token order: S <- decay[h] S + k v^T, o = S^T q.  p FP32 [T, N] with q, k (prepared) and v
-    at their columns; state FP32 [slots, H, dv, dk], updated in place; returns o FP32 [T, H dv].  chunked: the kernel for
-    prompt portions, which takes a request's tokens a chunk at a time (the same sums, regrouped)."""
+    at their columns; state FP32 [slots, H, dv, dk], updated in place; returns o FP32 [T, H dv]."""
     _need(p, "p", torch.float32)
     _need(decay, "decay", torch.float32, (H,))
     _need(state, "state", torch.float32)

@@ -79,7 +79,7 @@ class ParallelBlock(Block):
             raise TypeError(f"{type(self.mixer).__name__} adds into the stream itself; this arrangement needs its result")
         if self.ffn is None:
             return ScaledSum(self.scale, y)
-        if hasattr(self.ffn, "compute"):
+        if hasattr(self.ffn, "compute") and not getattr(self.ffn, "defers_add", False):
             return ScaledSum(self.scale, y, self.ffn.compute(x2, ctx))
         if self.ffn.defers_add:
             acc = None

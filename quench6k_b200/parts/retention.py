@@ -25,7 +25,6 @@ _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "gat
 @register_mixer("retention")
 class Retention(Mixer):
     graph_safe = True
-    chunk_beyond = 32            # steps whose longest portion has more tokens walk prompts a chunk at a time
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, v_dim: int, decay, eps: float, pos: PartSpec, k_scale=None, names=None):
         """decay: one number per head.  k_scale: what k is multiplied by after the rotation (default head_dim^-1/2)."""
@@ -35,8 +34,8 @@ class Retention(Mixer):
         self.D, self.H, self.dk, self.dv, self.decay, self.eps = hidden_size, num_heads, head_dim, v_dim, decay, float(eps)
         self.k_scale = float(k_scale) if k_scale is not None else head_dim ** -0.5
         self.pos = make_part(POSITION_ENCODINGS, "position encoding", pos)
-        if not self.pos.is_identity and self.pos.rotary_table is None:
-            raise ValueError("the retention kernels take a rotation of pairs or no position encoding")
+        if not self.pos.is_identity and self.pos.rotary_dim > head_dim:
+            raise ValueError(f"{self.pos.rotary_dim} turning dimensions in a head of {head_dim}")
         self.names = {**_NAMES, **(names or {})}
         # columns of the stacked product: [q | k | v | gate]
         self.k_col, self.v_col, self.g_col = num_heads * head_dim, 2 * num_heads * head_dim, 2 * num_heads * head_dim + num_heads * v_dim
@@ -76,8 +75,7 @@ class Retention(Mixer):
         ops.retention_prep(p, self.H, self.dk, 0, self.k_col, None if self.pos.is_identity else self.pos.rotary_table(), self.k_scale,
                            ctx.positions)
         ops.current_tag = "retention.recurrence"
-        o = ops.retention(p, 0, self.k_col, self.v_col, self.decay_t, state["S"], ctx.q_start, ctx.slot_ids, ctx.R, self.H, self.dk, self.dv,
-                          chunked=ctx.max_q_len > self.chunk_beyond)
+        o = ops.retention(p, 0, self.k_col, self.v_col, self.decay_t, state["S"], ctx.q_start, ctx.slot_ids, ctx.R, self.H, self.dk, self.dv)
         ops.current_tag = "retention.out"
         y = ops.delta_out(o, p, self.g_col, self.ones, self.eps, self.H, self.dv, rt.dtype)
         ops.current_tag = "retention.o"

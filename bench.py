@@ -252,6 +252,39 @@ def kernel_gated_delta(args):
     return 0
 
 
+def kernel_retention(args):
+    """The retention recurrence alone: one request's portion of --prefill-tokens tokens, 16 heads of 128 x 128, or --batch
+    requests of one token each (a decode step); CUDA events after warm-up.  Counted: 2 passes of 2 dk dv FLOPs per token
+    and head (the state's update and its product with q); bytes: the state read and written, q, k, v read and o written."""
+    import torch
+    from quench6k_b200 import ops
+    H, dk, dv, dev = 16, 128, 128, "cuda:0"
+    decode = bool(args.batch)
+    R, n = (args.batch, 1) if decode else (1, args.prefill_tokens)
+    T = R * n
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    p = torch.randn(T, 2 * H * dk + 2 * H * dv, device=dev) * 0.1
+    decay = 1.0 - 2.0 ** (-5.0 - 5.0 * torch.arange(H, device=dev, dtype=torch.float32) / H)
+    state = torch.zeros(R, H, dv, dk, device=dev)
+    q_start, slots = i32([i * n for i in range(R + 1)]), i32(list(range(R)))
+    run = lambda: ops.retention(p, 0, H * dk, 2 * H * dk, decay, state, q_start, slots, R, H, dk, dv)
+    for _ in range(max(3, args.warmup)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 4.0 * dk * dv * H * T
+    nbytes = 2.0 * 4 * H * dk * dv * R + 4.0 * T * H * (2 * dk + 2 * dv)
+    print(json.dumps({"kernel": "retention", "requests": R, "tokens_each": n, "us": round(ms * 1e3, 1), "ns_per_token": round(ms * 1e6 / n, 1),
+                      "gflops": round(flops / ms / 1e6, 1), "gbs": round(nbytes / ms / 1e6, 1), "steps": args.steps}))
+    return 0
+
+
 def profile_ops(args, runner, cfg_d, layers, ctx, stand_at_context, rand_ids):
     """Where the time of an eager decode step (batch --batch at the context) and of a prefill step goes, launcher by
     launcher: CUDA events around every launch (quench6k_b200.ops.profile_begin/profile_end), no profiler involved.  Eager
@@ -531,10 +564,11 @@ def main():
                          "(pedotar: dense feed-forwards; kipedra: windows and routed experts; sigusun: beside Kipedra and Pedotar) at equal layer sizes (--sizes), with each "
                          "model's time launcher by launcher (its own JSON line)")
     ap.add_argument("--sizes", default="s,m", help="--design: s (width 1024) and/or m (width 2048)")
-    ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gated_delta"],
+    ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gated_delta", "retention"],
                     help="time one kernel alone at the configuration's head sizes instead of the model: attention_prefill runs "
                          "--prefill-tokens query tokens that end at position --context (one request, contiguous pages); gated_delta runs "
-                         "the delta rule recurrence over one portion of --prefill-tokens tokens, or with --batch over that many single tokens")
+                         "the delta rule recurrence over one portion of --prefill-tokens tokens, or with --batch over that many single tokens; "
+                         "retention does the same for the retention recurrence")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -557,6 +591,8 @@ def main():
         return kernel_attention_prefill(args)
     if args.kernel == "gated_delta":
         return kernel_gated_delta(args)
+    if args.kernel == "retention":
+        return kernel_retention(args)
     if args.design:
         torch.cuda.set_device(0)
         return design_compare(args)

@@ -1221,9 +1221,12 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
             lib = library()
             lib.q6k_attention_flex_mma_talk_workspace.restype = ctypes.c_longlong
             ws = _workspace(lib.q6k_attention_flex_mma_talk_workspace(_i(T), _i(H), _i(Hkv), _i(dv)), k_pages.device, "flex")
-        elif ctas < 120 and not window and not chunk and max_context > 256:     # few row tiles: fixed key ranges over more CTAs
+        elif ctas < 120 and not chunk and max_context > 256:     # few row tiles: fixed key ranges over more CTAs
             want = max(1, 296 // ctas)
-            split_keys = max(256, (-(-max_context // want) + 63) // 64 * 64)
+            # under a window a tile sees its window and its own tokens: ranges sized for that span (the ranges that lie
+            # outside it cost a block that finds no key), and no more than 128 of them
+            span = min(max_context, window + attention_flex_tile_tokens(H, Hkv)) if window else max_context
+            split_keys = max(256, (-(-span // want) + 63) // 64 * 64, (-(-max_context // 128) + 63) // 64 * 64)
             nsplit = -(-max_context // split_keys)
             if nsplit > 1:
                 lib = library()

@@ -132,11 +132,11 @@ ONE = {
     "retention_wide_keys": (sc.retention(2, 136, 33, [0.995, 0.9], 136, 10000.0), 0),
     "retention_no_rotation": (sc.retention(1, 40, 8, [0.99], 0, 1.0), 3),
     "retention_and_experts": (sc.retention(2, 8, 8, [0.98, 1.0], 4, 50.0, ff=(5, 2, 20, 0.8, 12, 1.4)), 0),
-    "window": (sc.window(4, 8, 12, 10, 24, 1.5, 5, 100.0), 0),
+    "window": (sc.window(4, 8, 12, 10, 24, 0.6, 5, 100.0), 0),
     "window_of_pages": (sc.window(3, 16, 4, 4, 16, 2.0, 64, 10000.0), 0),
     "window_of_one": (sc.window(2, 16, 16, 16, 20, 1.0, 1, 50.0), 0),
     "window_never_reached": (sc.window(2, 40, 0, 40, 12, 1.5, 1000, 10000.0), 0),
-    "window_and_all_experts": (sc.window(2, 8, 8, 8, 16, 2.0, 6, 20.0, ff=(3, 3, 20, 1.0, None, 0)), 4),
+    "window_and_all_experts": (sc.window(2, 8, 8, 8, 16, 0.5, 6, 20.0, ff=(3, 3, 20, 1.0, None, 0)), 4),
     "sink": (sc.sink(3, 12, 4, 8, 20, 0.5, 3000.0), 0),
     "sink_and_one_expert": (sc.sink(2, 8, 8, 16, 40, 0.5, 100.0, ff=(4, 1, 12, 0.6, 8, 0.9)), 6),
 }

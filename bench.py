@@ -265,7 +265,7 @@ def kernel_retention(args):
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     p = torch.randn(T, 2 * H * dk + 2 * H * dv, device=dev) * 0.1
     decay = 1.0 - 2.0 ** (-5.0 - 5.0 * torch.arange(H, device=dev, dtype=torch.float32) / H)
-    state = torch.zeros(R, H, dv, dk, device=dev)
+    state = torch.zeros(R, H, dk, dv, device=dev)
     q_start, slots = i32([i * n for i in range(R + 1)]), i32(list(range(R)))
     run = lambda: ops.retention(p, 0, H * dk, 2 * H * dk, decay, state, q_start, slots, R, H, dk, dv)
     for _ in range(max(3, args.warmup)):

@@ -5,20 +5,21 @@
 //
 //  * retention_prep_kernel turns the first `rd` dimensions of every head of q and k by position * inv_freq[pair] (pairs by
 //    halves, or of neighbours) and multiplies k by a scale, in place on the FP32 result of the projection; a block per token.
-//  * retention_kernel walks a request's tokens in order.  A block owns 16 columns of one head of one request, a warp four of
-//    them (wide keys: two warps, half of the rows each): lane l holds rows l, l + 32, ... of its four columns in registers, so
-//    a token costs two shared-memory reads (k and q of a row) per twelve floating-point instructions.  The sums over the rows are left until eight tokens are done:
-//    the 32 partial sums a lane then holds (8 tokens x 4 columns) are summed over the lanes by one butterfly that halves
-//    the values with every stage (31 shuffles for all of them, and every value takes the same tree of additions, so a token's
-//    result does not depend on where in a tile it stands or where a prompt was cut).  q, k and v of eight tokens at a time
-//    are staged in shared memory, the next tile fetched into registers while this one is walked.
+//  * retention_kernel walks a request's tokens in order.  A block owns 16 columns of one head of one request; a thread holds
+//    a stretch of consecutive rows of ONE column in registers (lane = column and one of two stretches, eight warps = sixteen
+//    stretches), so k and q of its rows come as 16-byte reads every lane of a half-warp shares and a token costs three
+//    floating-point instructions per element of the state and little else.  A token's sum over the rows is the thread's own
+//    (in row order), then the two stretches of a warp (one shuffle), then the eight warps' through shared memory, in the
+//    warps' order: the same tree for every token wherever a prompt was cut.  q, k and v of eight tokens at a time are
+//    copied to shared memory asynchronously, three tiles ahead of the one that is walked (a tile's first read is a miss in
+//    L2 for one block of a head, and its latency is several times a tile's work).
 //
 // Everything is FP32: angles, the rotation, decays and their powers, the state and every sum.
 #include "common.cuh"
 
 namespace {
 
-constexpr int RET_WARPS = 4, RET_C = 4, RET_TILE = 8, RET_MAX_DK = 256;
+constexpr int RET_WARPS = 8, RET_THREADS = RET_WARPS * 32, RET_COLS = 16, RET_CHUNKS = 2 * RET_WARPS, RET_TILE = 8, RET_STAGES = 4, RET_MAX_DK = 256;
 
 // One block per token: the sines and cosines of its rd / 2 angles are made once (they are the same for every head, for q
 // and for k), then every pair of q and of k is turned in place and the rest of k scaled; what neither turns nor scales
@@ -50,137 +51,179 @@ __global__ void __launch_bounds__(256) retention_prep_kernel(float* p, int ld, i
     }
 }
 
-// grid (R, H, ceil(dv / 16)), 128 RS threads.  p: FP32 [T, ld] with q, k (prepared) and v at their columns; state: FP32
-// [slots, H, dv, dk] (a column's rows lie together); o: FP32 [T, H dv].  JN: rows per lane over the whole key (dk <= 32 JN);
-// RS: warps that share a column group, each with JN / RS of those rows (their sums meet in shared memory, in a fixed order).
-template <int JN, int RS>
-__global__ void __launch_bounds__(RET_WARPS * 32 * RS) retention_kernel(const float* p, int ld, int q_col, int k_col, int v_col, const float* decay,
-                                                                        float* state, const int* q_start, const int* slot_ids, float* o, int H,
-                                                                        int dk, int dv) {
+// Four bytes from global to shared memory without passing registers; `in` false writes a zero and reads nothing.
+__device__ __forceinline__ void ret_copy(float* dst, const float* src, bool in) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = in ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void ret_copy16(float* dst, const float* src, bool in) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = in ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+// grid (R, H, ceil(dv / 16)), 256 threads.  p: FP32 [T, ld] with q, k (prepared) and v at their columns; state: FP32
+// [slots, H, dk, dv]; o: FP32 [T, H dv].  RPT: rows per thread (dk <= 16 RPT).  STAGES tiles are in flight or in use.
+// WIDE: every head's q and k start on 16 bytes in every row of p and dk is a multiple of 4 (copies of 16 bytes).
+template <int RPT, int STAGES, bool WIDE>
+__global__ void __launch_bounds__(RET_THREADS) retention_kernel(const float* p, int ld, int q_col, int k_col, int v_col, const float* decay,
+                                                                float* state, const int* q_start, const int* slot_ids, float* o, int H,
+                                                                int dk, int dv) {
     pdl_enter();
-    constexpr int DKP = 32 * JN, JW = JN / RS, THREADS = RET_WARPS * 32 * RS, COLS = RET_WARPS * RET_C;
-    constexpr int PER_THREAD = RET_TILE * DKP / THREADS;                 // elements of q (and of k) a thread stages per tile
-    static_assert(JN % RS == 0 && RET_TILE * DKP % THREADS == 0, "rows divide among the warps, a tile among the threads");
-    static_assert(RET_TILE * RET_C == 32 && RET_TILE * COLS == RET_WARPS * 32, "one value per lane after the butterfly; one v per thread");
-    extern __shared__ __align__(16) float sm[];   // q [2][TILE][DKP] | k [2][TILE][DKP] | v [2][TILE][COLS] | sums [2][WARPS][32]
+    constexpr int DKP = RET_CHUNKS * RPT;                                // rows, padded
+    constexpr int PER_THREAD = RET_TILE * DKP / RET_THREADS;             // elements of q (and of k) a thread stages per tile
+    static_assert(RPT % 4 == 0 && RET_TILE * DKP % RET_THREADS == 0 && RET_TILE * RET_COLS <= RET_THREADS, "16-byte reads; a tile divides among the threads");
+    extern __shared__ __align__(16) float sm[];   // q [STAGES][TILE][DKP] | k likewise | v [STAGES][TILE][COLS] | sums [2][TILE][WARPS][COLS]
     float* qs = sm;
-    float* ks = qs + 2 * RET_TILE * DKP;
-    float* vs = ks + 2 * RET_TILE * DKP;
-    float* red = vs + 2 * RET_TILE * COLS;
-    const int r = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * COLS;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, cg = warp % RET_WARPS, rs = warp / RET_WARPS;
-    const int cw = c0 + cg * RET_C, row0 = rs * 32 * JW + lane;
+    float* ks = qs + STAGES * RET_TILE * DKP;
+    float* vs = ks + STAGES * RET_TILE * DKP;
+    float* red = vs + STAGES * RET_TILE * RET_COLS;
+    const int r = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * RET_COLS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, cl = lane % RET_COLS, col = c0 + cl;
+    const int row0 = (warp * 2 + lane / RET_COLS) * RPT;                 // this thread's first row
     const int t0 = q_start[r], t1 = q_start[r + 1];
+    if (t0 >= t1) return;
     const float d = decay[head];
-    float* cols = state + ((size_t)slot_ids[r] * H + head) * dv * dk;
-    float s[JW][RET_C];
+    float* mine = state + ((size_t)slot_ids[r] * H + head) * dk * dv + (col < dv ? col : 0);
+    float s[RPT];
 #pragma unroll
-    for (int j = 0; j < JW; ++j)
-#pragma unroll
-        for (int c = 0; c < RET_C; ++c) {
-            const int row = row0 + 32 * j;
-            s[j][c] = (cw + c < dv && row < dk) ? cols[(size_t)(cw + c) * dk + row] : 0.0f;
-        }
-    float fq[PER_THREAD], fk[PER_THREAD], fv = 0.0f;
-    auto fetch = [&](int ta) {                // this thread's share of the tile that starts at token ta, into registers
+    for (int i = 0; i < RPT; ++i) s[i] = (col < dv && row0 + i < dk) ? mine[(size_t)(row0 + i) * dv] : 0.0f;
+    auto fetch = [&](int ta, int b) {         // this thread's share of the tile that starts at token ta, on its way to buffer b
         const int n = min(RET_TILE, t1 - ta);
+        if (n > 0) {
+            if (WIDE) {
 #pragma unroll
-        for (int e = 0; e < PER_THREAD; ++e) {
-            const int i = threadIdx.x + e * THREADS, tt = i / DKP, row = i % DKP;
-            const bool in = tt < n && row < dk;
-            const float* src = p + (size_t)(ta + tt) * ld + (size_t)head * dk + row;
-            fq[e] = in ? src[q_col] : 0.0f;
-            fk[e] = in ? src[k_col] : 0.0f;
-        }
-        if (threadIdx.x < RET_TILE * COLS) {
-            const int tt = threadIdx.x / COLS, cc = c0 + threadIdx.x % COLS;
-            fv = (tt < n && cc < dv) ? p[(size_t)(ta + tt) * ld + v_col + (size_t)head * dv + cc] : 0.0f;
-        }
-    };
-    auto put = [&](int b) {
-#pragma unroll
-        for (int e = 0; e < PER_THREAD; ++e) {
-            const int i = threadIdx.x + e * THREADS;
-            qs[b * RET_TILE * DKP + i] = fq[e];
-            ks[b * RET_TILE * DKP + i] = fk[e];
-        }
-        if (threadIdx.x < RET_TILE * COLS) vs[b * RET_TILE * COLS + threadIdx.x] = fv;
-    };
-    if (t0 < t1) {
-        fetch(t0);
-        put(0);
-    }
-    __syncthreads();
-    int b = 0;
-    for (int ta = t0; ta < t1; ta += RET_TILE, b ^= 1) {
-        const int n = min(RET_TILE, t1 - ta);
-        const bool more = ta + RET_TILE < t1;
-        if (more) fetch(ta + RET_TILE);
-        float a[RET_TILE * RET_C];
-        if (cw < dv) {
-            const float* qb = qs + b * RET_TILE * DKP + row0;
-            const float* kb = ks + b * RET_TILE * DKP + row0;
-            const float* vb = vs + b * RET_TILE * COLS + cg * RET_C;
-#pragma unroll
-            for (int i = 0; i < RET_TILE * RET_C; ++i) a[i] = 0.0f;
-            auto token = [&](int tt) {
-                const float4 v = *reinterpret_cast<const float4*>(vb + tt * COLS);
-                const float vv[RET_C] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int j = 0; j < JW; ++j) {
-                    const float kk = kb[tt * DKP + 32 * j], qq = qb[tt * DKP + 32 * j];
-#pragma unroll
-                    for (int c = 0; c < RET_C; ++c) {
-                        s[j][c] = fmaf(d, s[j][c], kk * vv[c]);
-                        a[tt * RET_C + c] = fmaf(s[j][c], qq, a[tt * RET_C + c]);
+                for (int e = 0; e < (PER_THREAD + 3) / 4; ++e) {
+                    const int i = (threadIdx.x + e * RET_THREADS) * 4, tt = i / DKP, row = i % DKP;
+                    if (PER_THREAD >= 4 || i < RET_TILE * DKP) {
+                        const bool in = tt < n && row < dk;
+                        const float* src = in ? p + (size_t)(ta + tt) * ld + (size_t)head * dk + row : p;
+                        ret_copy16(qs + b * RET_TILE * DKP + i, src + (in ? q_col : 0), in);
+                        ret_copy16(ks + b * RET_TILE * DKP + i, src + (in ? k_col : 0), in);
                     }
                 }
-            };
-            if (n == RET_TILE) {              // a full tile: nothing stands between the tokens' loads and sums
-#pragma unroll
-                for (int tt = 0; tt < RET_TILE; ++tt) token(tt);
             } else {
 #pragma unroll
-                for (int tt = 0; tt < RET_TILE; ++tt)
-                    if (tt < n) token(tt);
-            }
-            // lane l ends with the sum over all lanes of value l (token l / 4 of the tile, column l % 4)
-#pragma unroll
-            for (int half = 16; half >= 1; half >>= 1) {
-                const bool up = (lane & half) != 0;
-#pragma unroll
-                for (int i = 0; i < half; ++i) {
-                    const float send = up ? a[i] : a[i + half];
-                    const float keep = up ? a[i + half] : a[i];
-                    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+                for (int e = 0; e < PER_THREAD; ++e) {
+                    const int i = threadIdx.x + e * RET_THREADS, tt = i / DKP, row = i % DKP;
+                    const bool in = tt < n && row < dk;
+                    const float* src = in ? p + (size_t)(ta + tt) * ld + (size_t)head * dk + row : p;
+                    ret_copy(qs + b * RET_TILE * DKP + i, src + (in ? q_col : 0), in);
+                    ret_copy(ks + b * RET_TILE * DKP + i, src + (in ? k_col : 0), in);
                 }
             }
-            if (rs > 0) red[(b * RET_WARPS + cg) * 32 + lane] = a[0];
+            if (threadIdx.x < RET_TILE * RET_COLS) {
+                const int tt = threadIdx.x / RET_COLS, cc = c0 + threadIdx.x % RET_COLS;
+                const bool in = tt < n && cc < dv;
+                ret_copy(vs + b * RET_TILE * RET_COLS + threadIdx.x, in ? p + (size_t)(ta + tt) * ld + v_col + (size_t)head * dv + cc : p, in);
+            }
         }
-        if (more) put(b ^ 1);
-        __syncthreads();
-        if (rs == 0 && cw < dv) {
-            const int tt = lane / RET_C, c = cw + lane % RET_C;
-            const float sum = RS > 1 ? a[0] + red[(b * RET_WARPS + cg) * 32 + lane] : a[0];
-            if (tt < n && c < dv) o[((size_t)(ta + tt) * H + head) * dv + c] = sum;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto finish = [&](int ta, int b2) {       // the warps' sums of one (token, column), in the warps' order
+        if (threadIdx.x < RET_TILE * RET_COLS) {
+            const int tt = threadIdx.x / RET_COLS, cc = threadIdx.x % RET_COLS;
+            if (ta + tt < t1 && c0 + cc < dv) {
+                const float* src = red + (b2 * RET_TILE + tt) * RET_WARPS * RET_COLS + cc;
+                float sum = src[0];
+#pragma unroll
+                for (int w = 1; w < RET_WARPS; ++w) sum += src[w * RET_COLS];
+                o[((size_t)(ta + tt) * H + head) * dv + c0 + cc] = sum;
+            }
+        }
+    };
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) fetch(t0 + st * RET_TILE, st);
+    int b = 0, b2 = 0;
+    for (int ta = t0; ta < t1; ta += RET_TILE, b = b + 1 == STAGES ? 0 : b + 1, b2 ^= 1) {
+        const int n = min(RET_TILE, t1 - ta);
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();                      // this tile has landed for everyone; the tile before it is done with
+        if (ta > t0) finish(ta - RET_TILE, b2 ^ 1);
+        fetch(ta + (STAGES - 1) * RET_TILE, b == 0 ? STAGES - 1 : b - 1);
+        const float* qb = qs + b * RET_TILE * DKP + row0;
+        const float* kb = ks + b * RET_TILE * DKP + row0;
+        const float* vb = vs + b * RET_TILE * RET_COLS + cl;
+        float* rb = red + (b2 * RET_TILE * RET_WARPS + warp) * RET_COLS + cl;
+        auto token = [&](int tt) {
+            const float v = vb[tt * RET_COLS];
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < RPT; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kb + tt * DKP + i);
+                const float4 q4 = *reinterpret_cast<const float4*>(qb + tt * DKP + i);
+                s[i] = fmaf(d, s[i], k4.x * v);
+                acc = fmaf(s[i], q4.x, acc);
+                s[i + 1] = fmaf(d, s[i + 1], k4.y * v);
+                acc = fmaf(s[i + 1], q4.y, acc);
+                s[i + 2] = fmaf(d, s[i + 2], k4.z * v);
+                acc = fmaf(s[i + 2], q4.z, acc);
+                s[i + 3] = fmaf(d, s[i + 3], k4.w * v);
+                acc = fmaf(s[i + 3], q4.w, acc);
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, RET_COLS);       // the lane with the same column and the warp's other rows
+            if (lane < RET_COLS) rb[tt * RET_WARPS * RET_COLS] = acc;
+        };
+        if (n == RET_TILE) {                  // a full tile: the next token's rows are read while this one's are summed
+            float4 kk[2][RPT / 4], qq[2][RPT / 4];
+            float vv[RET_TILE];
+#pragma unroll
+            for (int tt = 0; tt < RET_TILE; ++tt) vv[tt] = vb[tt * RET_COLS];
+#pragma unroll
+            for (int i = 0; i < RPT / 4; ++i) {
+                kk[0][i] = *reinterpret_cast<const float4*>(kb + 4 * i);
+                qq[0][i] = *reinterpret_cast<const float4*>(qb + 4 * i);
+            }
+#pragma unroll
+            for (int tt = 0; tt < RET_TILE; ++tt) {
+                if (tt + 1 < RET_TILE) {
+#pragma unroll
+                    for (int i = 0; i < RPT / 4; ++i) {
+                        kk[(tt + 1) & 1][i] = *reinterpret_cast<const float4*>(kb + (tt + 1) * DKP + 4 * i);
+                        qq[(tt + 1) & 1][i] = *reinterpret_cast<const float4*>(qb + (tt + 1) * DKP + 4 * i);
+                    }
+                }
+                const float v = vv[tt];
+                float acc = 0.0f;
+#pragma unroll
+                for (int i = 0; i < RPT / 4; ++i) {
+                    const float4 k4 = kk[tt & 1][i], q4 = qq[tt & 1][i];
+                    s[4 * i] = fmaf(d, s[4 * i], k4.x * v);
+                    acc = fmaf(s[4 * i], q4.x, acc);
+                    s[4 * i + 1] = fmaf(d, s[4 * i + 1], k4.y * v);
+                    acc = fmaf(s[4 * i + 1], q4.y, acc);
+                    s[4 * i + 2] = fmaf(d, s[4 * i + 2], k4.z * v);
+                    acc = fmaf(s[4 * i + 2], q4.z, acc);
+                    s[4 * i + 3] = fmaf(d, s[4 * i + 3], k4.w * v);
+                    acc = fmaf(s[4 * i + 3], q4.w, acc);
+                }
+                acc += __shfl_xor_sync(0xffffffffu, acc, RET_COLS);
+                if (lane < RET_COLS) rb[tt * RET_WARPS * RET_COLS] = acc;
+            }
+        } else {
+#pragma unroll
+            for (int tt = 0; tt < RET_TILE; ++tt)
+                if (tt < n) token(tt);
         }
     }
-    if (t0 < t1) {
+    __syncthreads();
+    finish(t0 + (t1 - t0 - 1) / RET_TILE * RET_TILE, b2 ^ 1);
+    if (col < dv) {
 #pragma unroll
-        for (int j = 0; j < JW; ++j)
-#pragma unroll
-            for (int c = 0; c < RET_C; ++c) {
-                const int row = row0 + 32 * j;
-                if (cw + c < dv && row < dk) cols[(size_t)(cw + c) * dk + row] = s[j][c];
-            }
+        for (int i = 0; i < RPT; ++i)
+            if (row0 + i < dk) mine[(size_t)(row0 + i) * dv] = s[i];
     }
 }
 
-template <int JN, int RS>
-void launch_retention(dim3 grid, cudaStream_t st, const float* p, int ld, int q_col, int k_col, int v_col, const float* decay, float* state,
-                      const int* q_start, const int* slot_ids, float* o, int H, int dk, int dv) {
-    const size_t smem = (size_t)(4 * RET_TILE * 32 * JN + 2 * RET_TILE * RET_WARPS * RET_C + 2 * RET_WARPS * 32) * sizeof(float);
-    q6k_launch(retention_kernel<JN, RS>, grid, RET_WARPS * 32 * RS, smem, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);
+template <int RPT, int STAGES, bool WIDE>
+int launch_retention(dim3 grid, cudaStream_t st, const float* p, int ld, int q_col, int k_col, int v_col, const float* decay, float* state,
+                     const int* q_start, const int* slot_ids, float* o, int H, int dk, int dv) {
+    const size_t smem = (size_t)(STAGES * RET_TILE * (2 * RET_CHUNKS * RPT + RET_COLS) + 2 * RET_TILE * RET_WARPS * RET_COLS) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(retention_kernel<RPT, STAGES, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    q6k_launch(retention_kernel<RPT, STAGES, WIDE>, grid, RET_THREADS, smem, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);
+    return 0;
 }
 
 }  // namespace
@@ -203,12 +246,18 @@ Q6K_API int q6k_retention(const float* p, int ld, int q_col, int k_col, int v_co
                           const int* slot_ids, int R, float* o, int H, int dk, int dv, cudaStream_t st) {
     if (R == 0) return 0;
     Q6K_REQUIRE(R > 0 && H > 0 && dk > 0 && dv > 0 && dk <= RET_MAX_DK, "retention: bad sizes R=%d H=%d dk=%d (at most %d) dv=%d", R, H, dk, RET_MAX_DK, dv);
-    const int zb = (dv + RET_WARPS * RET_C - 1) / (RET_WARPS * RET_C);
+    const int zb = (dv + RET_COLS - 1) / RET_COLS;
     Q6K_REQUIRE(H <= 65535 && zb <= 65535, "retention: grid too large");
     const dim3 grid(R, H, zb);
-    if (dk <= 32) launch_retention<1, 1>(grid, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);
-    else if (dk <= 64) launch_retention<2, 2>(grid, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);
-    else if (dk <= 128) launch_retention<4, 2>(grid, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);
-    else launch_retention<8, 2>(grid, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);
+    const bool wide = dk % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+#define RET_LAUNCH(RPT)                                                                                                               \
+    do {                                                                                                                              \
+        if (wide) launch_retention<RPT, RET_STAGES, true>(grid, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);       \
+        else launch_retention<RPT, RET_STAGES, false>(grid, st, p, ld, q_col, k_col, v_col, decay, state, q_start, slot_ids, o, H, dk, dv);           \
+    } while (0)
+    if (dk <= 64) RET_LAUNCH(4);
+    else if (dk <= 128) RET_LAUNCH(8);
+    else RET_LAUNCH(16);
+#undef RET_LAUNCH
     return q6k_check_launch("retention");
 }

@@ -1480,11 +1480,11 @@ def retention_prep(p: torch.Tensor, H: int, dk: int, q_col: int, k_col: int, rot
 def retention(p: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
               slot_ids: torch.Tensor, R: int, H: int, dk: int, dv: int) -> torch.Tensor:
     """Per request and head, in token order: S <- decay[h] S + k v^T, o = S^T q.  p FP32 [T, N] with q, k (prepared) and v
-    at their columns; state FP32 [slots, H, dv, dk], updated in place; returns o FP32 [T, H dv]."""
+    at their columns; state FP32 [slots, H, dk, dv], updated in place; returns o FP32 [T, H dv]."""
     _need(p, "p", torch.float32)
     _need(decay, "decay", torch.float32, (H,))
     _need(state, "state", torch.float32)
-    if tuple(state.shape[1:]) != (H, dv, dk) or p.dim() != 2 or max(q_col, k_col) + H * dk > p.shape[1] or v_col + H * dv > p.shape[1]:
+    if tuple(state.shape[1:]) != (H, dk, dv) or p.dim() != 2 or max(q_col, k_col) + H * dk > p.shape[1] or v_col + H * dv > p.shape[1]:
         raise KernelError("retention: shapes disagree")
     o = torch.empty((p.shape[0], H * dv), dtype=torch.float32, device=p.device)
     _call("q6k_retention", _ptr(p), _i(p.stride(0)), _i(q_col), _i(k_col), _i(v_col), _ptr(decay), _ptr(state), _ptr(q_start), _ptr(slot_ids),

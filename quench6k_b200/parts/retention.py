@@ -64,8 +64,7 @@ class Retention(Mixer):
         self.pos.bind(lambda name: get("position." + name), rt)
 
     def state_shape(self):
-        # the state is kept column-major: a column's rows lie together
-        return {"S": ((self.H, self.dv, self.dk), torch.float32)}
+        return {"S": ((self.H, self.dk, self.dv), torch.float32)}
 
     def forward(self, xn, ctx, cache, state, out):
         rt = self.rt

@@ -49,7 +49,7 @@ def test_retention_kernels_in_portions(H, dk, dv, rd):
                 o[t, h] = S.T @ q[t, h]
         want.append(o.view(n, H * dv))
     for cuts in ([[75], [22]], [[1, 2, 30, 1, 17, 24], [20, 2]], [[40, 3, 32], [1, 1, 20]]):
-        state = torch.zeros(4, H, dv, dk).cuda()
+        state = torch.zeros(4, H, dk, dv).cuda()
         state[1] = 7.0
         got, at = [[], []], [0, 0]
         for step in range(max(len(c) for c in cuts)):

@@ -63,7 +63,7 @@ def test_declared_tensors_caches_and_states():
     assert "l3.norm1" in names and "l3.norm2" not in names                  # no feed-forward, no second norm
     assert stored_name("l0.mlp.e3.up") == ("l0.mlp.experts.up", 3) and stored_name("l12.mlp.e10.gate") == ("l12.mlp.experts.gate", 10)
     assert stored_name("l0.mlp.shared.gate") is None and stored_name("l0.mlp.router") is None
-    assert model.state_shapes()[0] == {"S": ((3, 24, 16), torch.float32)}
+    assert model.state_shapes()[0] == {"S": ((3, 16, 24), torch.float32)}
     reqs = model.cache_requests()
     # layer 1's keys are read under its own window of 7 and layer 2's of 19: they are kept for the wider one
     assert reqs[0] is None and reqs[1].kind == "sliding" and reqs[1].window == 19 and reqs[2] is None and reqs[3].kind == "full"

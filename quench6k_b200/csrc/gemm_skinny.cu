@@ -33,7 +33,7 @@ enum { SK_STORE = 0, SK_ADD = 1, SK_SWIGLU = 2 };
 template <int NB, int RB, int EPI, int LOADS>
 __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx, int T_,
                                                                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ w2,
-                                                                    void* out, long long ldo, int N, int K, int k_slice, long long slice_stride, int act) {
+                                                                    void* out, long long ldo, int N, int K, int k_slice, long long slice_stride, int act, float limit) {
     // The weights are a model's and older than any kernel of the step: their first stretch is asked for while the kernel
     // launched before this one still runs (programmatic dependent launch); the activations and the output wait for it.
     pdl_launch();
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
         }
         if (n >= N || t >= T_) continue;
         const long long at = (long long)blockIdx.y * slice_stride + (long long)t * ldo + n;
-        if (EPI == SK_SWIGLU) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn((act == 0 ? s / (1.0f + __expf(-s)) : q6k_activation(s, act)) * s2);
+        if (EPI == SK_SWIGLU) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(act == 0 ? s / (1.0f + __expf(-s)) * s2 : q6k_gated(s, s2, act, limit));
         else if (EPI == SK_ADD) reinterpret_cast<float*>(out)[at] += s;
         else reinterpret_cast<float*>(out)[at] = s;
     }
@@ -142,11 +142,11 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
 
 template <int NB, int RB, int LOADS>
 int skinny_launch(int epi, cudaStream_t st, const __nv_bfloat16* x, long long ldx, int T_, const __nv_bfloat16* w, const __nv_bfloat16* w2, void* out,
-                  long long ldo, int N, int K, int slices, int k_slice, long long slice_stride, int act) {
+                  long long ldo, int N, int K, int slices, int k_slice, long long slice_stride, int act, float limit) {
     const dim3 grid((N + RB * 16 - 1) / (RB * 16), slices);
-    if (epi == SK_SWIGLU) q6k_launch_as(true, gemm_skinny_kernel<NB, 1, SK_SWIGLU, 4>, (N + 15) / 16, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, K, 0LL, act);
-    else if (epi == SK_ADD) q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_ADD, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, K, 0LL, act);
-    else q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_STORE, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, k_slice, slice_stride, act);
+    if (epi == SK_SWIGLU) q6k_launch_as(true, gemm_skinny_kernel<NB, 1, SK_SWIGLU, 4>, (N + 15) / 16, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, K, 0LL, act, limit);
+    else if (epi == SK_ADD) q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_ADD, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, K, 0LL, act, limit);
+    else q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_STORE, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, k_slice, slice_stride, act, limit);
     return q6k_check_launch("gemm_skinny");
 }
 
@@ -179,21 +179,21 @@ Q6K_API int q6k_gemm_skinny_slices(int tokens, int N, int K) {
 // [tokens, N] (epi 0 store, 1 add) or bfloat16 [tokens, N] (epi 2: silu(x w^T) * (x w2^T)), row pitch ldo.
 // slices > 1 (epi 0 only): K is cut into that many slices, slice z's sums go to out + z * slice_stride floats.
 Q6K_API int q6k_gemm_skinny(const void* x, long long ldx, int tokens, const void* w, const void* w2, int N, int K, void* out, long long ldo, int epi,
-                            int slices, long long slice_stride, cudaStream_t st) {
+                            float act_param, int slices, long long slice_stride, cudaStream_t st) {
     if (tokens == 0) return 0;
     Q6K_REQUIRE(tokens >= 1 && tokens <= 16, "gemm_skinny: %d tokens (1 to 16)", tokens);
     Q6K_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)w2 & 15) == 0,
                 "gemm_skinny: K=%d and the row pitch %lld must be multiples of 8 and the operands 16-byte aligned", K, ldx);
     const int act = epi >> 8;          // the activation of the gate (q6k_activation's code) above bit 8
     epi &= 255;
-    Q6K_REQUIRE(act >= 0 && act <= 2, "gemm_skinny: unknown activation %d", act);
+    Q6K_REQUIRE(act >= 0 && act <= Q6K_ACT_CLAMPED, "gemm_skinny: unknown activation %d", act);
     Q6K_REQUIRE(epi >= 0 && epi <= 2 && (epi == SK_SWIGLU) == (w2 != nullptr), "gemm_skinny: epilogue %d with%s a second matrix", epi, w2 ? "" : "out");
     Q6K_REQUIRE(slices >= 1 && (slices == 1 || epi == SK_STORE), "gemm_skinny: %d slices of K with epilogue %d", slices, epi);
     const int k_slice = slices == 1 ? K : ((K + slices - 1) / slices + 1023) / 1024 * 1024;
     const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *wp = (const __nv_bfloat16*)w, *w2p = (const __nv_bfloat16*)w2;
     // 32 rows per block where that still gives every SM two blocks; 16 otherwise
     const bool wide = N >= 148 * 2 * 32, deep = k_slice >= 4096 && !wide;          // long rows and few of them: eight loads per row at once
-#define SK_GO(NB_, RB_, LOADS_) skinny_launch<NB_, RB_, LOADS_>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K, slices, k_slice, slice_stride, act)
+#define SK_GO(NB_, RB_, LOADS_) skinny_launch<NB_, RB_, LOADS_>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K, slices, k_slice, slice_stride, act, act_param)
     if (tokens <= 8) {
         if (wide) return SK_GO(1, 2, 4);
         if (deep) return SK_GO(1, 1, 8);

@@ -524,8 +524,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = N
         if out is not None or epi != EPI_STORE:
             raise KernelError("gemm_skinny: slices of K are for plain products into scratch")
         out = _workspace(slices * T * N * 4, x.device)[: slices * T * N].view(slices, T, N)
-        _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(N), _i(epi), _i(slices),
-              _ll(T * N), _stream())
+        _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(N), _i(epi), _f(_act_param(act)),
+              _i(slices), _ll(T * N), _stream())
         return out
     if out is None:
         if accumulate:
@@ -534,8 +534,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = N
     _need(out, "out", out_dtype)
     if out.shape[0] < T or out.shape[1] != N:
         raise KernelError(f"gemm_skinny: out has shape {tuple(out.shape)}, needs [{T}, {N}]")
-    _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(out.stride(0)), _i(epi), _i(1),
-          _ll(0), _stream())
+    _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(out.stride(0)), _i(epi), _f(_act_param(act)),
+          _i(1), _ll(0), _stream())
     return out
 
 

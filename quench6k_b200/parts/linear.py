@@ -40,10 +40,10 @@ def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = N
 def swiglu_matmul(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, rt, act=None) -> torch.Tensor:
     """y[r] = act(a[r] @ w_gate^T) * (a[r] @ w_up^T) in a's dtype; act None: silu."""
     if _tc(a, w_gate, rt):
-        few = not ops.act_has_param(act)          # the kernels for a few tokens take activations without a constant
-        if few and ops.gemv_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
+        # the kernel for one or two tokens takes activations without a constant
+        if not ops.act_has_param(act) and ops.gemv_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
             return ops.gemv(a, w_gate, w2=w_up, act=act)
-        if few and ops.gemm_skinny_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
+        if ops.gemm_skinny_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
             return ops.gemm_skinny(a, w_gate, w2=w_up, act=act)
         return ops.gemm_tc(a, w_gate, w2=w_up, act=act)
     return ops.gemm_simt(a, w_gate, w2=w_up, act=act)

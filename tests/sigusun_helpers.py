@@ -63,7 +63,7 @@ def plain(cfg_d, weights, tokens, forced=None):
     return plain_sigusun.forward(cfg_d, weights, tokens, forced=forced)
 
 
-def replay_and_compare(folder, cfg, weights, requests, steps, max_tokens, dtype, what, page=None, max_requests=4):
+def replay_and_compare(folder, cfg, weights, requests, steps, max_tokens, dtype, what, page=None, max_requests=4, tol=None):
     """Replays the steps through the engine and compares every request with the plain implementation.  A mixture of experts
     is discontinuous (a rounding that flips a near-tie of two router logits moves a position by far more than rounding), so
     the engine reports the experts it chose and the plain implementation is run on those; how often its own choice would
@@ -80,7 +80,7 @@ def replay_and_compare(folder, cfg, weights, requests, steps, max_tokens, dtype,
             for p, chosen in plain_sigusun.forward.chosen.items():
                 flips += int((chosen.sort(-1).values != forced[p].sort(-1).values).any(-1).sum())
                 positions += len(toks)
-        worst = max(worst, assert_close(got[rid], want, dtype, f"{what} {dtype} {rid}"))
+        worst = max(worst, assert_close(got[rid], want, dtype, f"{what} {dtype} {rid}", tol=tol))
     assert flips <= (0.002 if dtype == "float32" else 0.05) * positions + 1, f"{what} {dtype}: {flips} of {positions} choices of experts differ"
     print(f"{what} {dtype}: worst error {worst:.3e}, {flips} of {positions} choices of experts differ")
     return got

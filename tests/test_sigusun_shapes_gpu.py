@@ -1,0 +1,87 @@
+"""Sigusun configurations drawn at random over everything config.json allows (any order of the three kinds of layer, any
+head counts, key, value, latent and rotated widths that are multiples of 16 or not, widths and vocabularies that are no
+multiple of 8, rotations of none, part or all of a retention head, decays up to one, windows from one position to longer
+than any prompt, layers that read the latent of any earlier layer that makes one, under wider and narrower windows or
+none, experts from two up with one to all of them chosen, with and without a shared expert, layers without a
+feed-forward, models with and without the per-layer token input, pages of odd sizes), each replayed in mixed batches with
+reused pages and slots in float32 and bfloat16 against the plain implementation: a size the kernels do not take must be
+handed to a kernel that does, never computed wrongly."""
+import random
+
+import pytest
+
+import helpers
+import sigusun_helpers as sh
+
+pytestmark = pytest.mark.gpu
+
+
+def draw(seed, tensor_core=False):
+    rng = random.Random(seed)
+    n_layers = rng.choice([1, 2, 3, 4, 5, 6])
+    even = lambda hi: 2 * rng.randint(0, hi // 2)
+
+    def feed_forward():
+        if rng.random() < 0.25:
+            return None
+        experts = rng.choice([2, 3, 5, 8, 9, 17])
+        out = {"kind": "moe", "expert": {"ff": rng.choice([8, 12, 24, 40, 64]), "limit": rng.choice([0.3, 1.0, 2.5, 7.0])},
+               "router": {"experts": experts, "top": rng.randint(1, min(experts, 5))}}
+        if rng.random() < 0.6:
+            out["shared"] = {"ff": rng.choice([8, 20, 48, 96]), "limit": rng.choice([0.5, 1.5, 7.0])}
+        return out
+
+    def retention():
+        heads = rng.choice([1, 2, 3, 4, 6])
+        dim = rng.choice([16, 32, 64, 128]) if tensor_core else rng.choice([6, 8, 16, 24, 32, 40, 64, 100])
+        vdim = dim if rng.random() < 0.4 else rng.choice([4, 8, 12, 16, 32, 48, 64])
+        return {"type": "retention", "mlp": feed_forward(),
+                "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": [rng.choice([1.0, 1.0 - 2.0 ** -rng.randint(3, 10)]) for _ in range(heads)],
+                          "rot": {"base": rng.choice([50.0, 10000.0, 1e6]), "dims": rng.choice([0, 2, even(dim), dim // 2 * 2])}}}
+
+    layers, lenders = [], []
+    for i in range(n_layers):
+        kind = rng.choice(["retention", "latent_attention", "latent_attention", "latent_attention_2"])
+        if kind == "retention":
+            layers.append(retention())
+            continue
+        heads = rng.choice([1, 2, 3, 4, 6, 8])
+        if tensor_core:
+            dim, vdim, rank, rot_dim = rng.choice([16, 32, 64]), rng.choice([16, 32, 64]), rng.choice([32, 64, 128]), rng.choice([0, 16, 32, 64])
+        else:
+            dim, vdim, rank, rot_dim = rng.choice([4, 6, 8, 16, 24, 40]), rng.choice([4, 5, 8, 16, 24, 33]), rng.choice([7, 8, 16, 24, 40, 64]), even(24)
+        m = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": rank, "rot_dim": rot_dim, "scale": rng.choice([0.05, 0.125, 0.3]),
+             "rot": {"base": rng.choice([50.0, 10000.0, 1e6]), "dims": rot_dim}}
+        if lenders and rng.random() < 0.45:                           # reads an earlier layer's latent: its widths and rotation
+            j = rng.choice(lenders)
+            src = layers[j]["mixer"]
+            m.update(kv_from=j, kv_rank=src["kv_rank"], rot_dim=src["rot_dim"], rot=dict(src["rot"]))
+        else:
+            lenders.append(i)
+        if kind == "latent_attention":
+            m["mask"] = {"size": rng.choice([1, 2, 7, 16, 30, 64, 500])}
+        layers.append({"type": kind, "mixer": m, "mlp": feed_forward()})
+    cfg = {"architecture": "Sigusun", "vocab": rng.choice([17, 100, 257, 1001]), "width": rng.choice([24, 40, 72, 100, 136, 264]),
+           "norm": {"eps": rng.choice([1e-6, 1e-5, 3e-4])}, "kv_page_size": rng.choice([1, 3, 4, 8, 16, 24, 32]), "layers": layers}
+    if tensor_core:
+        cfg["width"], cfg["vocab"], cfg["kv_page_size"] = rng.choice([64, 128, 256]), rng.choice([128, 256, 1000]), rng.choice([8, 16, 32])
+    if rng.random() < 0.6:
+        cfg["token_side"] = {"dim": rng.choice([1, 3, 8, 16, 24])}
+    return cfg
+
+
+# the last six at sizes the tensor-core products and attention kernels take
+@pytest.mark.parametrize("seed,tensor_core", [(s, False) for s in range(14)] + [(s, True) for s in range(14, 20)])
+def test_random_configuration(tmp_path, seed, tensor_core):
+    cfg = draw(seed, tensor_core)
+    cfg_d, weights = sh.make_folder(str(tmp_path), cfg, seed=seed, init_std=0.08)
+    V, page = cfg["vocab"], cfg["kv_page_size"]
+    rng = random.Random(100 + seed)
+    reqs = {f"r{i}": helpers.random_tokens(rng.randint(3, 90), V, 7 * seed + i) for i in range(5)}
+    steps, mt = helpers.schedule_mixed(reqs, page, seed=seed, max_live=3)
+    # float32 holds the exact comparison; in bfloat16 the operands' rounding, magnified by the norms on the sublayers'
+    # results, reaches a tenth of the largest logit in the deeper of these models: twice the usual allowance there
+    for dtype, tol in (("float32", None), ("bfloat16", 0.08)):
+        sh.replay_and_compare(str(tmp_path), cfg_d, weights, reqs, steps, mt, dtype, f"configuration {seed}: {cfg}", max_requests=3, tol=tol)
+    from quench6k_b200 import ops
+    assert ops.tc_status() == 0

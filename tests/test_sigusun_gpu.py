@@ -396,6 +396,18 @@ def test_long_decoding(model, dtype):
     sh.replay_and_compare(model["folder"], model["cfg"], model["weights"], reqs, steps, mt, dtype, model["name"] + " long decode")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt(model, dtype):
+    """A prompt of 1,300 tokens whole, in portions, and with its last tokens decoded: windows and the causal layers' key
+    ranges at lengths several times the short requests', a recurrent state a thousand tokens old."""
+    if model["name"] not in ("G1", "G3"):
+        pytest.skip("two of the models are enough for the length (the plain implementation is slow)")
+    reqs = {"p": helpers.random_tokens(1300, model["cfg"]["vocab"], 21)}
+    for what, (steps, mt) in {"whole": helpers.schedule_whole(reqs), "portions": helpers.schedule_portions(reqs, seed=8),
+                              "tail": helpers.schedule_tail(reqs, tail=40)}.items():
+        sh.replay_and_compare(model["folder"], model["cfg"], model["weights"], reqs, steps, mt, dtype, f"{model['name']} long prompt {what}")
+
+
 def test_greedy_generation_through_the_engine(model):
     """Engine.generate (scheduler, continuous batching, device-side argmax, CUDA graphs) against greedy decoding with the
     plain implementation, float32; prompts of unequal length in one engine with few pages."""

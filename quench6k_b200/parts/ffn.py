@@ -147,7 +147,7 @@ class RoutedExperts(FeedForward):
         T = xn.shape[0]
         pairs = T * self.k
         defer = defer and (self.shared is None or routed_only)
-        if (self.gated and not self.own_router and rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
+        if (self.gated and self.act == "silu" and not self.own_router and rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
                 and ops.tc_supported(xn, self.w_gate) and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
             # (token, slot) pair straight from the selection, no permutation and no gather
@@ -156,13 +156,12 @@ class RoutedExperts(FeedForward):
             if self.routing_tap is not None:
                 self._tap(ctx, sel_e, logits)
             ops.current_tag = "experts.gate_up"
-            gate = None if self.act == "silu" else self.act
-            if gate is None and ops.gemv_preferred(T, self.I, self.D):    # a token or two: the matrix-vector kernel per pair (silu gates)
+            if ops.gemv_preferred(T, self.I, self.D):                     # a token or two: the matrix-vector kernel per pair
                 act = ops.gemv(xn, self.w_gate, w2=self.w_up, pair_expert=sel_e.view(-1), pair_div=self.k)
                 ops.current_tag = "experts.down"
                 y = ops.gemv(act, self.w_down, pair_expert=sel_e.view(-1), pair_div=1, pairs_are_old=True)   # the router made them, two kernels ago
             else:
-                act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order, act=gate)  # [pairs, I]
+                act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)  # [pairs, I]
                 ops.current_tag = "experts.down"
                 y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order, pairs_are_old=True)   # FP32 [pairs, D]
             if defer:

@@ -6,5 +6,6 @@ from .models import flint as _flint       # noqa: F401  (registers FlintForCausa
 from .models import pedotar as _pedotar   # noqa: F401  (registers Pedotar)
 from .models import kipedra as _kipedra   # noqa: F401  (registers Kipedra)
 from .models import sigusun as _sigusun   # noqa: F401  (registers Sigusun)
+from .models import kitodra as _kitodra   # noqa: F401  (registers Kitodra)
 from .sampling.params import SamplingParams      # noqa: F401
 from .engine.engine import Engine, RequestOutput   # noqa: F401

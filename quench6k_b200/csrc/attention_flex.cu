@@ -61,7 +61,15 @@ struct FlexArgs {
     void* out; int out_head_major;
     int T_, H, Hkv;
     const float* sinks;                 // [H] or null: exp(sinks[h]) joins head h's softmax denominator (no key, no value, not scaled)
+    float softcap;                      // > 0: a scaled score s becomes softcap * tanh(s / softcap)
+    int maps;                           // > 1: every head attends `maps` times with keys of its own over the same values: q holds
+                                        // heads x maps rows per token (a head's maps side by side), the key pages Hkv = groups x maps
+                                        // heads (a group's maps side by side), the value pages one head per group
+    float* out_f32;                     // not null: the result leaves as FP32 here instead of through `out`
 };
+
+// The query row (of H per token) that key head kh serves as the g-th of its G, and the value head that goes with kh.
+__device__ __forceinline__ int flex_query_head(int kh, int g, int G, int maps) { return maps > 1 ? ((kh / maps) * G + g) * maps + kh % maps : kh * G + g; }
 
 template <typename T>
 __device__ __forceinline__ void load_query(const FlexArgs& a, int t, int h, float* q) {
@@ -84,12 +92,12 @@ __global__ void __launch_bounds__(128) attention_flex_kernel(const FlexArgs a) {
     const int lo = first_visible(pos, a.window, a.chunk);
     float* qw = qs + warp * dk;
     const T* kp = (const T*)a.k_pages + (size_t)kh * a.k_head_stride;
-    const T* vp = (const T*)a.v_pages + (size_t)kh * a.v_head_stride;
+    const T* vp = (const T*)a.v_pages + (size_t)(a.maps > 1 ? kh / a.maps : kh) * a.v_head_stride;
     const bool vec = dk % Vec<T>::n == 0 && ((size_t)a.k_ld * sizeof(T)) % 16 == 0 && ((size_t)kp % 16) == 0;
     T* out = (T*)a.out;
 
     for (int g = warp; g < G; g += nwarps) {
-        const int h = kh * G + g;
+        const int h = flex_query_head(kh, g, G, a.maps);
         load_query<T>(a, t, h, qw);
         __syncwarp();
         float m = -INFINITY, l = 0.0f, o[DPL];
@@ -103,6 +111,7 @@ __global__ void __launch_bounds__(128) attention_flex_kernel(const FlexArgs a) {
             if (ok) {
                 rowi = bt[j / a.page_size] * a.page_size + j % a.page_size;
                 s = dot_row<T>(qw, kp + (size_t)rowi * a.k_ld, dk, vec) * a.scale;
+                if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
             }
             const float mn = fmaxf(m, warp_max(s));     // finite: the tile holds at least one visible key
             const float corr = m == -INFINITY ? 0.0f : expf(m - mn);
@@ -135,7 +144,10 @@ __global__ void __launch_bounds__(128) attention_flex_kernel(const FlexArgs a) {
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
             const int d = lane + 32 * i;
-            if (d < a.dv) out[orow * a.dv + d] = from_f32<T>(o[i] * inv);
+            if (d < a.dv) {
+                if (a.out_f32) a.out_f32[orow * a.dv + d] = o[i] * inv;
+                else out[orow * a.dv + d] = from_f32<T>(o[i] * inv);
+            }
         }
         __syncwarp();
     }
@@ -254,15 +266,15 @@ __device__ __forceinline__ float rotated(const float* x, int d, int rd, int neig
     return first ? x[d] * cs - x[partner] * sn : x[d] * cs + x[partner] * sn;
 }
 
-// qkv: FP32 [T, ld] = [Hq heads of hd | Hkv heads of hd | Hkv heads of vd].  Per-head RMS norm of q and k (weights or
+// qkv: FP32 [T, ld] = [Hq heads of hd | Hkv heads of hd | Hv heads of vd].  Per-head RMS norm of q and k (weights or
 // null), rotation of their first rd dimensions (inv_freq or null), q -> q_out [T, Hq, hd]; k, v -> pages
-// [Hkv, num_pages, page_size, hd] and [.., vd].  Grid (T, Hq + 2 Hkv) (or (T, Hq) when nothing is written).
+// [Hkv, num_pages, page_size, hd] and [Hv, .., vd].  Grid (T, Hq + Hkv + Hv) (or (T, Hq) when nothing is written).
 template <typename T>
 __global__ void __launch_bounds__(128) qkv_pages_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, int hd, int vd,
                                                         const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rd,
                                                         int neighbours, const int* positions, const int* req_of_token,
                                                         const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out,
-                                                        T* k_pages, T* v_pages) {
+                                                        T* k_pages, T* v_pages, int Hv) {
     pdl_enter();
     extern __shared__ float xs[];            // max(hd, vd) floats
     __shared__ float red[32];
@@ -349,22 +361,51 @@ __global__ void heads_to_rows_kernel(const float* src, T* out, int H, int T_, in
     out[i] = from_f32<T>(src[((size_t)h * T_ + t) * n + d]);
 }
 
+// The two maps of a head combined: a FP32 [T, H, 2, dv] (a head's maps side by side) -> out [T, H dv] in the storage type,
+// o = a1 - lambda a2, then o / sqrt(mean(o^2) + eps) * mult over the head's dv values.  A warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128) map_difference_kernel(const float* a, T* out, int rows, int dv, float lambda, float eps, float mult) {
+    pdl_enter();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* a1 = a + (size_t)row * 2 * dv;
+    const float* a2 = a1 + dv;
+    float ss = 0.0f;
+    for (int d = lane; d < dv; d += 32) {
+        const float o = a1[d] - lambda * a2[d];
+        ss = fmaf(o, o, ss);
+    }
+    const float inv = rsqrtf(warp_sum(ss) / (float)dv + eps) * mult;
+    for (int d = lane; d < dv; d += 32) out[(size_t)row * dv + d] = from_f32<T>((a1[d] - lambda * a2[d]) * inv);
+}
+
 }  // namespace
+
+Q6K_API int q6k_map_difference(const float* a, void* out, int T_, int H, int dv, float lambda, float eps, float mult, int dtype, cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && H > 0 && dv > 0, "map_difference: bad sizes T=%d H=%d dv=%d", T_, H, dv);
+    const long long rows = (long long)T_ * H;
+    Q6K_REQUIRE(rows <= 0x7fffffffLL, "map_difference: too many rows");
+    Q6K_DISPATCH(dtype, q6k_launch(map_difference_kernel<T>, dim3((unsigned)((rows + 3) / 4)), 128, 0, st, a, (T*)out, (int)rows, dv, lambda, eps, mult););
+    return q6k_check_launch("map_difference");
+}
 
 Q6K_API int q6k_attention_flex(const float* qa, int da, const void* qb, int db, int q_head_major, const void* k_pages,
                                long long k_head_stride, int k_ld, const void* v_pages, long long v_head_stride, int v_ld, int dv,
                                const int* block_table, int max_blocks, int page_size, const int* req_of_token, const int* positions,
                                int window, int chunk, float scale, const float* talk, const float* sinks, void* out, int out_head_major,
-                               int T_, int H, int Hkv, int dtype, cudaStream_t st) {
+                               int T_, int H, int Hkv, int dtype, float softcap, int maps, float* out_f32, cudaStream_t st) {
     if (T_ == 0) return 0;
     const int dk = da + db;
+    Q6K_REQUIRE(maps >= 1 && Hkv % maps == 0 && softcap >= 0.0f, "attention: %d maps over %d key heads, softcap %f", maps, Hkv, softcap);
+    Q6K_REQUIRE(!talk || (maps == 1 && softcap == 0.0f && !out_f32), "attention with mixed heads takes neither maps, a cap nor FP32 results");
     Q6K_REQUIRE(T_ > 0 && H > 0 && Hkv > 0 && H % Hkv == 0, "attention: bad head counts H=%d Hkv=%d", H, Hkv);
     Q6K_REQUIRE(da >= 0 && db >= 0 && dk > 0 && (da == 0 || qa) && (db == 0 || qb), "attention: bad query parts %d + %d", da, db);
     Q6K_REQUIRE(dv > 0 && dv <= MAX_DV, "attention: value width %d outside 1..%d", dv, MAX_DV);
     Q6K_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0, "attention: bad page_size %d / max_blocks %d / window %d / chunk %d",
                 page_size, max_blocks, window, chunk);
     FlexArgs a{qa, da, qb, db, q_head_major, k_pages, k_head_stride, k_ld, v_pages, v_head_stride, v_ld, dv, block_table, max_blocks,
-               page_size, req_of_token, positions, window, chunk, scale, talk, out, out_head_major, T_, H, Hkv, sinks};
+               page_size, req_of_token, positions, window, chunk, scale, talk, out, out_head_major, T_, H, Hkv, sinks, softcap, maps, out_f32};
     if (talk) {
         Q6K_REQUIRE(!sinks, "attention with mixed heads takes no sinks");
         Q6K_REQUIRE(dv <= 256 && H <= 64, "attention with mixed heads: value width %d (at most 256), %d heads (at most 64)", dv, H);
@@ -389,18 +430,19 @@ Q6K_API int q6k_attention_flex(const float* qa, int da, const void* qb, int db, 
 Q6K_API int q6k_qkv_pages(const float* qkv, int ld, int splits, long long split_stride, int T_, int Hq, int Hkv, int hd, int vd,
                           const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rotary_dim, int neighbours,
                           const int* positions, const int* req_of_token, const int* block_table, int max_blocks, int page_size,
-                          int num_pages, void* q_out, void* k_pages, void* v_pages, int write_kv, int dtype, cudaStream_t st) {
+                          int num_pages, void* q_out, void* k_pages, void* v_pages, int write_kv, int dtype, int Hv, cudaStream_t st) {
     if (T_ == 0) return 0;
+    if (Hv <= 0) Hv = Hkv;
     Q6K_REQUIRE(T_ > 0 && Hq > 0 && Hkv > 0 && hd > 0 && vd > 0 && splits >= 1, "qkv_pages: bad sizes T=%d Hq=%d Hkv=%d hd=%d vd=%d", T_, Hq, Hkv, hd, vd);
     Q6K_REQUIRE(!inv_freq || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= hd), "qkv_pages: %d rotating dimensions of a head of %d", rotary_dim, hd);
     Q6K_REQUIRE(!write_kv || (page_size > 0 && max_blocks > 0), "qkv_pages: bad page_size %d / max_blocks %d", page_size, max_blocks);
-    const int heads = write_kv ? Hq + 2 * Hkv : Hq;
+    const int heads = write_kv ? Hq + Hkv + Hv : Hq;
     Q6K_REQUIRE(heads <= 65535, "qkv_pages: %d heads exceed the grid limit", heads);
     const size_t smem = (size_t)(hd > vd ? hd : vd) * sizeof(float);
     Q6K_REQUIRE(smem <= 48 * 1024, "qkv_pages: heads of %d do not fit shared memory", hd > vd ? hd : vd);
     Q6K_DISPATCH(dtype, q6k_launch(qkv_pages_kernel<T>, dim3(T_, heads), 128, smem, st, qkv, ld, splits, (size_t)split_stride, Hq, Hkv, hd, vd,
                                    q_norm, k_norm, eps, inv_freq, inv_freq ? rotary_dim : 0, neighbours, positions, req_of_token, block_table,
-                                   max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages););
+                                   max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, Hv););
     return q6k_check_launch("qkv_pages");
 }
 

@@ -43,7 +43,13 @@ struct MmaArgs {
     int nbuf;                           // 2: the next key tile is fetched (cp.async) while this one is used; 1: one buffer
     int v_heads;                        // > 0 (mixed heads): blockIdx.z is the value head and part_o is [T, H, v_heads, dv]
     const float* sinks;                 // [H] or null: exp(sinks[h]) joins head h's softmax denominator (with split keys, in the merge)
+    float softcap;                      // > 0: a scaled score s becomes softcap * tanh(s / softcap)
+    int maps;                           // > 1: every head attends `maps` times with keys of its own over the same values (see
+                                        // attention_flex.cu): q rows heads x maps, key heads groups x maps, value heads groups
+    float* out_f32;                     // not null: the result leaves as FP32 here instead of through `out`
 };
+
+__device__ __forceinline__ int mma_query_head(int kh, int g, int G, int maps) { return maps > 1 ? ((kh / maps) * G + g) * maps + kh % maps : kh * G + g; }
 
 __device__ __forceinline__ int first_visible_mma(int pos, int window, int chunk) {
     int lo = 0;
@@ -99,7 +105,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
     int* row_lo = row_pos + ROWS;                                               // [ROWS]
     int* key_rows = row_lo + ROWS;                                              // [2][KEYS]
 
-    const int tile = blockIdx.x, kh = blockIdx.y, split = a.v_heads > 0 ? 0 : blockIdx.z, vh = a.v_heads > 0 ? blockIdx.z : kh;
+    const int tile = blockIdx.x, kh = blockIdx.y, split = a.v_heads > 0 ? 0 : blockIdx.z, vh = a.v_heads > 0 ? blockIdx.z : a.maps > 1 ? kh / a.maps : kh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tok0 = a.tile_tok0[tile], ntok = a.tile_ntok[tile];
     const int* bt = a.block_table + (size_t)a.req_of_token[tok0] * a.max_blocks;
@@ -118,7 +124,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
         const int tk = r / G, g = r % G;
         __align__(16) __nv_bfloat16 v[8];
         if (tk < ntok && tk < tokens) {
-            const int t = tok0 + tk, h = kh * G + g;
+            const int t = tok0 + tk, h = mma_query_head(kh, g, G, a.maps);
             const size_t row = a.q_head_major ? (size_t)h * a.T_ + t : (size_t)t * a.H + h;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -242,7 +248,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
                 for (int e = 0; e < 2; ++e) {
                     const int kk = warp * 8 + qc + e, j = j0 + kk;
                     const bool ok = j >= lo && j <= pos && key_row[kk] >= 0;
-                    const float v = ok ? s[mb][hf * 2 + e] * a.scale : -INFINITY;
+                    float v = ok ? s[mb][hf * 2 + e] * a.scale : -INFINITY;
+                    if (ok && a.softcap > 0.0f) v = a.softcap * tanhf(v / a.softcap);
                     s[mb][hf * 2 + e] = v;
                     mx = fmaxf(mx, v);
                 }
@@ -336,7 +343,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
             const int r = mb * 16 + qr + hf * 8;
             const int tk = r / G, g = r % G;
             if (tk >= ntok || tk >= tokens) continue;
-            const int t = tok0 + tk, h = kh * G + g;
+            const int t = tok0 + tk, h = mma_query_head(kh, g, G, a.maps);
             if (a.v_heads > 0) {
                 const float inv = l_run[mb][hf] > 0.0f ? 1.0f / l_run[mb][hf] : 0.0f;
                 float* dst = a.part_o + (((size_t)t * a.H + h) * a.v_heads + vh) * a.dv;
@@ -368,8 +375,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     const int d = (warp * NB + nb) * 8 + qc;
-                    if (d < a.dv)
-                        *reinterpret_cast<__nv_bfloat162*>(a.out + orow * a.dv + d) = __floats2bfloat162_rn(o[mb][nb][hf * 2] * inv, o[mb][nb][hf * 2 + 1] * inv);
+                    if (d < a.dv) {
+                        if (a.out_f32) *reinterpret_cast<float2*>(a.out_f32 + orow * a.dv + d) = make_float2(o[mb][nb][hf * 2] * inv, o[mb][nb][hf * 2 + 1] * inv);
+                        else *reinterpret_cast<__nv_bfloat162*>(a.out + orow * a.dv + d) = __floats2bfloat162_rn(o[mb][nb][hf * 2] * inv, o[mb][nb][hf * 2 + 1] * inv);
+                    }
                 }
             }
         }
@@ -378,7 +387,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
 
 // Merges the key ranges of one (token, head) in order: out = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s.
 __global__ void __launch_bounds__(128) attention_flex_merge_kernel(const float* part_o, const float* part_ml, int nsplit, int T_, int H, int dv,
-                                                                   __nv_bfloat16* out, int out_head_major, const float* sinks) {
+                                                                   __nv_bfloat16* out, int out_head_major, const float* sinks, float* out_f32) {
     pdl_enter();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t row = (size_t)t * H + h, stride = (size_t)T_ * H;
@@ -397,7 +406,8 @@ __global__ void __launch_bounds__(128) attention_flex_merge_kernel(const float* 
             const float m = part_ml[(s * stride + row) * 2];
             if (m != -INFINITY) acc = fmaf(expf(m - M), part_o[(s * stride + row) * dv + d], acc);
         }
-        out[orow * dv + d] = __float2bfloat16_rn(acc * inv);
+        if (out_f32) out_f32[orow * dv + d] = acc * inv;
+        else out[orow * dv + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -445,8 +455,10 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
                                    const int* block_table, int max_blocks, int page_size, const int* req_of_token, const int* positions,
                                    const int* tile_tok0, const int* tile_ntok, int n_tiles, int window, int chunk, float scale, void* out,
                                    int out_head_major, int T_, int H, int Hkv, int nsplit, int split_keys, float* workspace,
-                                   const float* talk, const float* sinks, cudaStream_t st) {
+                                   const float* talk, const float* sinks, float softcap, int maps, float* out_f32, cudaStream_t st) {
     if (T_ == 0 || n_tiles == 0) return 0;
+    Q6K_REQUIRE(maps >= 1 && Hkv % maps == 0 && softcap >= 0.0f, "attention_flex_mma: %d maps over %d key heads, softcap %f", maps, Hkv, softcap);
+    Q6K_REQUIRE(!talk || (maps == 1 && softcap == 0.0f && !out_f32), "attention_flex_mma: mixed heads take neither maps, a cap nor FP32 results");
     const int dk = da + db;
     const bool shared_v = v_pages == k_pages && v_ld == k_ld && v_head_stride == k_head_stride;
     Q6K_REQUIRE(q6k_attention_flex_mma_supported(H, Hkv, dk, dv, k_ld, v_ld, db, shared_v), "attention_flex_mma: shapes H=%d Hkv=%d dk=%d dv=%d not taken", H, Hkv, dk, dv);
@@ -458,7 +470,7 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
               (const __nv_bfloat16*)v_pages, v_head_stride, v_ld, dv, block_table, max_blocks, page_size, req_of_token, positions,
               tile_tok0, tile_ntok, window, chunk, scale, (__nv_bfloat16*)out, out_head_major,
               workspace, workspace ? workspace + (size_t)nsplit * T_ * H * dv : nullptr, split_keys, nsplit, T_, H, Hkv,
-              flex_mma_smem(dk, dv, shared_v, 2) <= 220 * 1024 ? 2 : 1, talk ? Hkv : 0, sinks};
+              flex_mma_smem(dk, dv, shared_v, 2) <= 220 * 1024 ? 2 : 1, talk ? Hkv : 0, sinks, softcap, maps, out_f32};
     const size_t smem = flex_mma_smem(dk, dv, shared_v, a.nbuf);
     const int nb = ((dv + 7) / 8 + WARPS - 1) / WARPS;
     dim3 grid(n_tiles, Hkv, talk ? Hkv : nsplit);
@@ -479,7 +491,7 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
     }
     if (nsplit > 1) {
         q6k_launch(attention_flex_merge_kernel, dim3(T_, H), 128, 0, st, (const float*)a.part_o, (const float*)a.part_ml, nsplit, T_, H, dv,
-                   (__nv_bfloat16*)out, out_head_major, sinks);
+                   (__nv_bfloat16*)out, out_head_major, sinks, out_f32);
         return q6k_check_launch("attention_flex_merge");
     }
     return 0;

@@ -18,6 +18,41 @@ __global__ void embed_kernel(const int* tokens, const T* table, float* h, int D,
     for (int i = threadIdx.x; i < D; i += blockDim.x) h[(size_t)t * D + i] = to_f32(row[i]);
 }
 
+// The token-pair embedding: h[t] += table[row(t)], row = (previous token * mul_prev + token * mul_cur) mod buckets (64-bit
+// arithmetic), or row `buckets` (the table's last) for a request's first token.  The token before a portion's first row is
+// the request's state (prev [slots]: the last token of its earlier portions); the block of that row reads it and then
+// stores the portion's last token there (no other block touches the slot).  Token ids -(i + 1) stand for fed[i] as in embed.
+__device__ __forceinline__ int fed_token(const int* tokens, int t, const int* fed, int n_fed) {
+    int tok = tokens[t];
+    if (tok < 0 && fed != nullptr && -tok - 1 < n_fed) tok = fed[-tok - 1];
+    return tok < 0 ? 0 : tok;
+}
+
+template <typename T>
+__global__ void embed_pair_kernel(const int* tokens, const T* table, float* h, int D, int buckets, unsigned long long mul_prev,
+                                  unsigned long long mul_cur, const int* positions, const int* req_of_token, const int* q_start,
+                                  const int* slot_ids, int* prev, const int* fed, int n_fed) {
+    pdl_enter();
+    __shared__ int row_s;
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const int r = req_of_token[t], first = q_start[r], pos = positions[t];
+        const int cur = fed_token(tokens, t, fed, n_fed);
+        int before = 0;
+        if (t == first) {
+            int* mine = prev + slot_ids[r];
+            before = *mine;
+            *mine = fed_token(tokens, q_start[r + 1] - 1, fed, n_fed);
+        } else {
+            before = fed_token(tokens, t - 1, fed, n_fed);
+        }
+        row_s = pos == 0 ? buckets : (int)(((unsigned long long)before * mul_prev + (unsigned long long)cur * mul_cur) % (unsigned long long)buckets);
+    }
+    __syncthreads();
+    const T* row = table + (size_t)row_s * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) h[(size_t)t * D + i] += to_f32(row[i]);
+}
+
 // out[r] = T(x[row] * rsqrt(mean(x[row]^2) + eps) * w), row = rows ? rows[r] : r.  Sum of squares,
 // rsqrt and the products are FP32; the per-thread partial sums and the block sum run in a fixed order.
 // With `add`, x[row] += add[r] first and the sum is written back (the residual add of the block,
@@ -193,6 +228,16 @@ Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, in
     Q6K_REQUIRE(T_ > 0 && D > 0 && V > 0 && n_fed >= 0, "embed: bad sizes T=%d D=%d V=%d", T_, D, V);
     Q6K_DISPATCH(dtype, q6k_launch(embed_kernel<T>, T_, 256, 0, st, tokens, (const T*)table, h, D, V, fed, n_fed););
     return q6k_check_launch("embed");
+}
+
+Q6K_API int q6k_embed_pair(const int* tokens, const void* table, float* h, int T_, int D, int buckets, long long mul_prev, long long mul_cur,
+                           const int* positions, const int* req_of_token, const int* q_start, const int* slot_ids, int* prev, int dtype,
+                           const int* fed, int n_fed, cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && D > 0 && buckets > 0 && mul_prev >= 0 && mul_cur >= 0 && n_fed >= 0, "embed_pair: bad sizes T=%d D=%d buckets=%d", T_, D, buckets);
+    Q6K_DISPATCH(dtype, q6k_launch(embed_pair_kernel<T>, T_, 256, 0, st, tokens, (const T*)table, h, D, buckets, (unsigned long long)mul_prev,
+                                   (unsigned long long)mul_cur, positions, req_of_token, q_start, slot_ids, prev, fed, n_fed););
+    return q6k_check_launch("embed_pair");
 }
 
 // add: FP32 [R, D] or null; when given, x[row] += add[r] is stored before normalising (rows must then be null).

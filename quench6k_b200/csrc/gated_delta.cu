@@ -22,7 +22,8 @@
 //    The state is kept column-major, [slots, heads, dv, dk]: a column's rows lie together.
 //
 //    delta_out_kernel closes the mixer: every head's o is divided by its root mean square over dv, multiplied by a
-//    weight shared by the heads and by silu of a gate projection, and leaves in the operand dtype for the output product.
+//    weight shared by the heads and by silu (or the sigmoid) of a gate projection, and leaves in the operand dtype for the
+//    output product.  Called with ONE head of all heads' values it norms them together.
 #include "common.cuh"
 
 namespace {
@@ -36,6 +37,8 @@ constexpr int DELTA_TILE = 16;       // tokens whose inputs are staged in shared
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+// what the output gate passes through: 0 silu, 1 sigmoid
+__device__ __forceinline__ float gate_f(float v, int gate) { return gate == 1 ? 1.0f / (1.0f + expf(-v)) : silu_f(v); }
 
 // the projected value of row `row`, channel c: the slices in order, then the bias
 __device__ __forceinline__ float projected(const float* x, int slices, size_t slice_stride, int ldx, const float* bias, size_t row, int c) {
@@ -364,7 +367,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) gated_delta_kernel(const float*
 // values and gates in registers, all loads asked for before the sum; wider ones read the row twice.
 template <typename T>
 __global__ void __launch_bounds__(128) delta_out_kernel(const float* o, const float* p, int ldp, int g_col, const float* w, float eps, T* out,
-                                                        int H, int dv) {
+                                                        int H, int dv, int gate) {
     pdl_enter();
     const int t = blockIdx.x, head = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= H) return;
@@ -386,7 +389,7 @@ __global__ void __launch_bounds__(128) delta_out_kernel(const float* o, const fl
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int i = lane + 32 * j;
-            if (i < dv) dst[i] = from_f32<T>(v[j] * inv * ww[j] * silu_f(g[j]));
+            if (i < dv) dst[i] = from_f32<T>(v[j] * inv * ww[j] * gate_f(g[j], gate));
         }
         return;
     }
@@ -394,7 +397,7 @@ __global__ void __launch_bounds__(128) delta_out_kernel(const float* o, const fl
     for (int i = lane; i < dv; i += 32) ss = fmaf(orow[i], orow[i], ss);
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)dv + eps);
-    for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(orow[i] * inv * w[i] * silu_f(grow[i]));
+    for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(orow[i] * inv * w[i] * gate_f(grow[i], gate));
 }
 
 }  // namespace
@@ -460,10 +463,10 @@ Q6K_API int q6k_gated_delta(float* u, int ldu, const float* p, int ldp, int b_co
 }
 
 Q6K_API int q6k_delta_out(const float* o, const float* p, int ldp, int g_col, const float* w, float eps, void* out, int T_, int H, int dv, int dtype,
-                          cudaStream_t st) {
+                          int gate, cudaStream_t st) {
     if (T_ == 0) return 0;
-    Q6K_REQUIRE(T_ > 0 && H > 0 && dv > 0, "delta_out: bad sizes T=%d H=%d dv=%d", T_, H, dv);
+    Q6K_REQUIRE(T_ > 0 && H > 0 && dv > 0 && (gate == 0 || gate == 1), "delta_out: bad sizes T=%d H=%d dv=%d gate=%d", T_, H, dv, gate);
     Q6K_REQUIRE((H + 3) / 4 <= 65535, "delta_out: %d heads exceed the grid limit", H);
-    Q6K_DISPATCH(dtype, q6k_launch(delta_out_kernel<T>, dim3(T_, (H + 3) / 4), 128, 0, st, o, p, ldp, g_col, w, eps, (T*)out, H, dv););
+    Q6K_DISPATCH(dtype, q6k_launch(delta_out_kernel<T>, dim3(T_, (H + 3) / 4), 128, 0, st, o, p, ldp, g_col, w, eps, (T*)out, H, dv, gate););
     return q6k_check_launch("delta_out");
 }

@@ -5,6 +5,7 @@
 //
 //  * retention_prep_kernel turns the first `rd` dimensions of every head of q and k by position * inv_freq[pair] (pairs by
 //    halves, or of neighbours) and multiplies k by a scale, in place on the FP32 result of the projection; a block per token.
+//    Before that it may pass the row's first `act_cols` columns (q, k and v of a mixer that activates them) through silu.
 //  * retention_kernel walks a request's tokens in order.  A block owns 16 columns of one head of one request; a thread holds
 //    a stretch of consecutive rows of ONE column in registers (lane = column and one of two stretches, eight warps = sixteen
 //    stretches), so k and q of its rows come as 16-byte reads every lane of a half-warp shares and a token costs three
@@ -26,14 +27,18 @@ constexpr int RET_WARPS = 8, RET_THREADS = RET_WARPS * 32, RET_COLS = 16, RET_CH
 // is not touched.
 __global__ void __launch_bounds__(256) retention_prep_kernel(float* p, int ld, int H, int dk, int q_col, int k_col,
                                                              const float* inv_freq, int rd, int neighbours, float k_scale,
-                                                             const int* positions) {
+                                                             const int* positions, int act_cols) {
     pdl_enter();
     extern __shared__ float xs[];            // cos [rd / 2] | sin [rd / 2]
     const int t = blockIdx.x, half = rd / 2;
     const float pos = (float)positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &xs[half + i], &xs[i]);
-    __syncthreads();
     float* row = p + (size_t)t * ld;
+    for (int c = threadIdx.x; c < act_cols; c += blockDim.x) {             // silu on the projections, before anything else
+        const float z = row[c];
+        row[c] = z / (1.0f + expf(-z));
+    }
+    __syncthreads();
     for (int w = threadIdx.x; w < 2 * H * half; w += blockDim.x) {          // (q or k, head, pair)
         const int i = w % half, h = (w / half) % H, is_k = w / (half * H);
         float* x = row + (is_k ? k_col : q_col) + (size_t)h * dk;
@@ -232,13 +237,15 @@ Q6K_API int q6k_retention_max_dim() { return RET_MAX_DK; }
 
 // Rotates q and k of every head in place and scales k.
 Q6K_API int q6k_retention_prep(float* p, int ld, int T_, int H, int dk, int q_col, int k_col,
-                               const float* inv_freq, int rd, int neighbours, float k_scale, const int* positions, cudaStream_t st) {
+                               const float* inv_freq, int rd, int neighbours, float k_scale, const int* positions, int act_cols,
+                               cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && H > 0 && dk > 0 && 2 * H <= 65535, "retention_prep: bad sizes T=%d H=%d dk=%d", T_, H, dk);
     Q6K_REQUIRE(rd >= 0 && rd % 2 == 0 && rd <= dk && (rd == 0 || inv_freq), "retention_prep: %d turning dimensions of %d", rd, dk);
-    if (rd == 0 && k_scale == 1.0f) return 0;
+    Q6K_REQUIRE(act_cols >= 0 && act_cols <= ld, "retention_prep: %d activated columns of %d", act_cols, ld);
+    if (rd == 0 && k_scale == 1.0f && act_cols == 0) return 0;
     q6k_launch(retention_prep_kernel, dim3(T_), 256, (size_t)rd * sizeof(float), st, p, ld, H, dk, q_col, k_col,
-               inv_freq, rd, neighbours, k_scale, positions);
+               inv_freq, rd, neighbours, k_scale, positions, act_cols);
     return q6k_check_launch("retention_prep");
 }
 

@@ -143,17 +143,20 @@ __global__ void activate_kernel(const float* x, int ldx, T* out, int I, size_t c
 }
 
 // One warp per token: scores s = sigmoid(logits), the k largest of s + bias (ties to the lower index), weights
-// s / (sum of the chosen s + 1e-20) * scale.  logits: [slices, T, E], summed in order.  Shared memory: E floats a warp (the
-// choice values) and E more (the scores).
+// s / (sum of the chosen s + 1e-20) * scale, or s * scale when renorm is 0.  logits: [slices, T, E], summed in order.
+// groups > 1: the experts form `groups` equal groups of neighbours; a group's worth is the sum of its two largest choice
+// values (its one value, if it has one expert), and only experts of the `keep` groups of most worth (ties to the lower
+// index) can be chosen.  Shared memory: E floats a warp (the choice values), E more (the scores) and `groups` more.
 __global__ void route_biased_kernel(const float* logits, int slices, size_t slice_stride, const float* bias, float scale, int T_, int E, int k,
-                                    int* sel_e, float* sel_w) {
+                                    int* sel_e, float* sel_w, int renorm, int groups, int keep) {
     pdl_enter();
     extern __shared__ float sc[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int t = blockIdx.x * warps + warp;
     if (t >= T_) return;
-    float* choice = sc + (size_t)warp * 2 * E;
+    float* choice = sc + (size_t)warp * (2 * E + groups);
     float* score = choice + E;
+    float* worth = score + E;
     for (int e = lane; e < E; e += 32) {
         float z = logits[(size_t)t * E + e];
         for (int s = 1; s < slices; ++s) z += logits[s * slice_stride + (size_t)t * E + e];
@@ -162,6 +165,39 @@ __global__ void route_biased_kernel(const float* logits, int slices, size_t slic
         choice[e] = bias ? sg + bias[e] : sg;
     }
     __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {                              // a lane per group: its two largest choice values
+            float a = -INFINITY, b = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float c = choice[e];
+                if (c > a) b = a, a = c;
+                else if (c > b) b = c;
+            }
+            worth[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        for (int j = 0; j < keep; ++j) {                                       // the kept groups are marked by +inf
+            float best = -INFINITY;
+            int best_g = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float c = worth[g];
+                if (c != INFINITY && (c > best || (c == best && g < best_g) || best_g == 0x7fffffff)) best = c, best_g = g;
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+                const int og = __shfl_xor_sync(0xffffffffu, best_g, off);
+                if (og != 0x7fffffff && (best_g == 0x7fffffff || ob > best || (ob == best && og < best_g))) best = ob, best_g = og;
+            }
+            __syncwarp();
+            if (lane == 0 && best_g < groups) worth[best_g] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (worth[e / per] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
     float sum = 0.0f, mine = 0.0f;
     int mine_e = 0;
     for (int j = 0; j < k; ++j) {
@@ -188,7 +224,7 @@ __global__ void route_biased_kernel(const float* logits, int slices, size_t slic
         if (lane == 0) choice[best_e] = -INFINITY;
         __syncwarp();
     }
-    const float den = sum + 1e-20f;
+    const float den = renorm ? sum + 1e-20f : 1.0f;
     // every lane's last result, then the earlier ones it parked in memory
     const int last = lane < k ? ((k - 1 - lane) >> 5) * 32 + lane : -1;
     if (last >= 0) sel_w[(size_t)t * k + last] = mine, sel_e[(size_t)t * k + last] = mine_e;
@@ -228,12 +264,14 @@ Q6K_API int q6k_activate(const float* x, int ldx, void* out, int rows, int I, in
 }
 
 Q6K_API int q6k_route_biased(const float* logits, int slices, const float* bias, float scale, int T_, int E, int k, int* sel_e, float* sel_w,
-                             cudaStream_t st) {
+                             int renorm, int groups, int keep, cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && E > 0 && k > 0 && k <= E && slices >= 1, "route_biased: bad sizes T=%d E=%d k=%d slices=%d", T_, E, k, slices);
     Q6K_REQUIRE(E <= 4096, "route_biased: %d experts exceed the supported 4096", E);
+    Q6K_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && k <= keep * (E / groups),
+                "route_biased: %d experts in %d groups, %d kept, %d chosen", E, groups, keep, k);
     const int warps = E <= 1024 ? 4 : 1;
-    q6k_launch(route_biased_kernel, (T_ + warps - 1) / warps, warps * 32, (size_t)warps * 2 * E * sizeof(float), st, logits, slices, (size_t)T_ * E, bias,
-               scale, T_, E, k, sel_e, sel_w);
+    q6k_launch(route_biased_kernel, (T_ + warps - 1) / warps, warps * 32, (size_t)warps * (2 * E + groups) * sizeof(float), st, logits, slices,
+               (size_t)T_ * E, bias, scale, T_, E, k, sel_e, sel_w, renorm, groups, keep);
     return q6k_check_launch("route_biased");
 }

@@ -71,7 +71,8 @@ class ModelRunner:
                 lead, dt = (r.kv_heads, pages[g] + 1, page_size), r.dtype or rt.dtype
                 k = torch.zeros((*lead, r.head_dim), dtype=dt, device=rt.device)
                 # values that are the first entries of the key rows get no pages of their own: a view into the keys'
-                v = k[..., :r.v_dim] if r.values_in_keys else torch.zeros((*lead, r.v_dim or r.head_dim), dtype=dt, device=rt.device)
+                v = (k[..., :r.v_dim] if r.values_in_keys else
+                     torch.zeros((r.v_heads or r.kv_heads, *lead[1:], r.v_dim or r.head_dim), dtype=dt, device=rt.device))
                 self.caches.append(LayerCache(g, k, v, page_size))
 
         def state_for(s):

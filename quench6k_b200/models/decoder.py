@@ -13,7 +13,7 @@ import torch
 
 from .. import ops
 from ..parts import linear
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheRequest, LayerCache, Runtime, WeightedRows, make_part,
+from ..parts.base import (BLOCKS, EMBED_ADDS, FEED_FORWARDS, MIXERS, NORMS, CacheRequest, LayerCache, Runtime, WeightedRows, make_part,
                           to_operand)
 from ..spec import ModelSpec, TensorSpec
 
@@ -29,7 +29,7 @@ class DecoderModel:
             norm1 = make_part(NORMS, "norm", ls.norm, size=D)
             mixer = make_part(MIXERS, "mixer", ls.mixer, hidden_size=D)
             ffn = make_part(FEED_FORWARDS, "feed-forward", ls.ffn, hidden_size=D) if ls.ffn is not None else None
-            norm2 = make_part(NORMS, "norm", ls.norm, size=D) if ffn is not None else None
+            norm2 = make_part(NORMS, "norm", ls.norm, size=D) if ffn is not None and not ls.shared_norm else None
             after = {}
             if ls.post_norm is not None:
                 after["norm1b"] = make_part(NORMS, "norm", ls.post_norm, size=D)
@@ -39,6 +39,7 @@ class DecoderModel:
                 after["side"] = make_part(FEED_FORWARDS, "feed-forward", ls.side, hidden_size=D)
             self.blocks.append(BLOCKS[ls.block](norm1, mixer, norm2, ffn, **after, **ls.block_params))
         self.embed_norm = make_part(NORMS, "norm", spec.embed_norm, size=D) if spec.embed_norm is not None else None
+        self.embed_add = make_part(EMBED_ADDS, "embedding add", spec.embed_add, hidden_size=D) if spec.embed_add is not None else None
         self.final_norm = make_part(NORMS, "norm", spec.final_norm, size=D)
         self.order = list(spec.order)
         self.kv_source = list(spec.kv_source)
@@ -53,6 +54,8 @@ class DecoderModel:
     def tensors(self) -> List[TensorSpec]:
         s = self.spec
         out = [TensorSpec(s.embed_name, (s.vocab_size, s.hidden_size))]
+        if self.embed_add is not None:
+            out += [TensorSpec(s.embed_add_prefix + t.name, t.shape, t.role, t.init) for t in self.embed_add.tensors()]
         if self.embed_norm is not None:
             out += [TensorSpec(s.embed_norm_prefix + t.name, t.shape, t.role, t.init) for t in self.embed_norm.tensors()]
         if s.side_table is not None:
@@ -74,11 +77,12 @@ class DecoderModel:
         return out
 
     def state_shapes(self):
-        """Per executed position: the shape of its mixer's fixed-size per-request state, or None."""
-        return [self.blocks[i].mixer.state_shape() for i in self.order]
+        """Per executed position: the shape of its mixer's fixed-size per-request state, or None; one more entry, the state of
+        what the model adds to its embedding output, if it has such a part."""
+        return [self.blocks[i].mixer.state_shape() for i in self.order] + ([self.embed_add.state_shape()] if self.embed_add is not None else [])
 
     def graph_safe(self) -> bool:
-        parts = [self.final_norm] + ([self.embed_norm] if self.embed_norm is not None else [])
+        parts = [self.final_norm] + [x for x in (self.embed_norm, self.embed_add) if x is not None]
         for b in self.blocks:
             parts += [part for _, part in b.parts()]
         return all(getattr(x, "graph_safe", False) for x in parts)
@@ -88,6 +92,8 @@ class DecoderModel:
         s = self.spec
         self.rt = rt
         self.embed = to_operand(get(s.embed_name), rt)
+        if self.embed_add is not None:
+            self.embed_add.bind(lambda n: get(s.embed_add_prefix + n), rt)
         if self.embed_norm is not None:
             self.embed_norm.bind(lambda n: get(s.embed_norm_prefix + n), rt)
         self.side_table = to_operand(get(s.side_table[0]), rt) if s.side_table is not None else None
@@ -104,6 +110,9 @@ class DecoderModel:
         [len(ctx.logit_rows), vocab] or None when no row is wanted."""
         ops.current_tag = "embedding"
         h = ops.embed(ctx.token_ids, self.embed, fed=ctx.fed)
+        if self.embed_add is not None:
+            ops.current_tag = "embedding.add"
+            self.embed_add.forward(h, ctx, states[len(self.order)])
         if self.embed_norm is not None:
             ops.current_tag = "norm.embedding"
             self.embed_norm.normalize(h)

@@ -140,6 +140,26 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor]
     return out
 
 
+def embed_pair(h: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, mul_prev: int, mul_cur: int, positions: torch.Tensor,
+               req_of_token: torch.Tensor, q_start: torch.Tensor, slot_ids: torch.Tensor, prev: torch.Tensor,
+               fed: Optional[torch.Tensor] = None) -> None:
+    """h[t] += float32(table[row]) in place, row = (token before * mul_prev + token * mul_cur) mod buckets with buckets =
+    rows of the table - 1, or the table's last row for a request's first token (position 0).  The token before a portion's
+    first row is prev[slot] (int32 [slots]), which then takes the portion's last token.  `fed` as in embed."""
+    T = tokens.numel()
+    _need(h, "h", torch.float32, (T, table.shape[1]))
+    _need(tokens, "tokens", torch.int32)
+    _need(table, "table")
+    _need(prev, "prev", torch.int32)
+    if fed is not None:
+        _need(fed, "fed", torch.int32)
+    if table.shape[0] < 2 or mul_prev < 0 or mul_cur < 0:
+        raise KernelError("embed_pair: the table needs a bucket and its last row, the multipliers may not be negative")
+    _call("q6k_embed_pair", _ptr(tokens), _ptr(table), _ptr(h), _i(T), _i(table.shape[1]), _i(table.shape[0] - 1), _ll(mul_prev), _ll(mul_cur),
+          _ptr(positions), _ptr(req_of_token), _ptr(q_start), _ptr(slot_ids), _ptr(prev), _i(dtype_code(table.dtype)), _ptr(fed),
+          _i(fed.numel() if fed is not None else 0), _stream())
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
             out: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None, weighted=None) -> torch.Tensor:
     """out[r] = out_dtype(x[row] * rsqrt(mean(x[row]^2) + eps) * w); row = rows[r] if given.
@@ -1118,9 +1138,10 @@ def selective_scan_segments(q_lens, device):
 
 def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_norm, eps: float, rotary, positions: torch.Tensor,
               req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int, k_pages: Optional[torch.Tensor],
-              v_pages: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
-    """qk_prep for keys and values of different widths: qkv FP32 [T, Hq hd + Hkv hd + Hkv vd] (or split-K slices of it);
-    q -> [T, Hq, hd]; k -> pages [Hkv, P, page, hd]; v -> pages [Hkv, P, page, vd]."""
+              v_pages: Optional[torch.Tensor], out_dtype: torch.dtype, v_heads: Optional[int] = None) -> torch.Tensor:
+    """qk_prep for keys and values of different widths: qkv FP32 [T, Hq hd + Hkv hd + Hv vd] (or split-K slices of it);
+    q -> [T, Hq, hd]; k -> pages [Hkv, P, page, hd]; v -> pages [Hv, P, page, vd].  v_heads: Hv, if it is not Hkv."""
+    Hv = v_heads or Hkv
     _need(qkv, "qkv", torch.float32)
     splits, split_stride = 1, 0
     if qkv.dim() == 3:
@@ -1132,9 +1153,10 @@ def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_
         _need(k_pages, "k_pages", out_dtype)
         _need(v_pages, "v_pages", out_dtype)
         _need(block_table, "block_table", torch.int32)
-        if tuple(k_pages.shape[2:]) != (page_size, hd) or tuple(v_pages.shape[2:]) != (page_size, vd) or k_pages.shape[0] != Hkv:
+        if (tuple(k_pages.shape[2:]) != (page_size, hd) or tuple(v_pages.shape[2:]) != (page_size, vd) or k_pages.shape[0] != Hkv
+                or v_pages.shape[0] != Hv or v_pages.shape[1] != k_pages.shape[1]):
             raise KernelError("qkv_pages: the pages do not match the heads")
-    if qkv.shape[1] < Hq * hd + (Hkv * (hd + vd) if write else 0):
+    if qkv.shape[1] < Hq * hd + (Hkv * hd + Hv * vd if write else 0):
         raise KernelError("qkv_pages: qkv rows are too short")
     inv_freq, rotary_dim, neighbours = rotary if rotary is not None else (None, 0, False)
     q = torch.empty((T, Hq, hd), dtype=out_dtype, device=qkv.device)
@@ -1142,7 +1164,7 @@ def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_
           _ptr(k_norm), _f(eps), _ptr(inv_freq), _i(rotary_dim), _i(1 if neighbours else 0), _ptr(positions), _ptr(req_of_token),
           _ptr(block_table), _i(block_table.shape[1] if block_table is not None else 1), _i(page_size),
           _i(k_pages.shape[1] if write else 0), _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(1 if write else 0),
-          _i(dtype_code(out_dtype)), _stream())
+          _i(dtype_code(out_dtype)), _i(Hv), _stream())
     return q
 
 
@@ -1180,14 +1202,19 @@ def heads_to_rows(src: torch.Tensor, H: int, out_dtype: torch.dtype) -> torch.Te
 def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], head_major: bool, k_pages: torch.Tensor, v_pages: torch.Tensor,
                    block_table: torch.Tensor, req_of_token: torch.Tensor, positions: torch.Tensor, H: int, scale: float,
                    window: Optional[int] = None, chunk: Optional[int] = None, talk: Optional[torch.Tensor] = None,
-                   out_head_major: bool = False, tiles=None, max_context: int = 0, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out_head_major: bool = False, tiles=None, max_context: int = 0, sinks: Optional[torch.Tensor] = None,
+                   softcap: float = 0.0, maps: int = 1, out_f32: bool = False) -> torch.Tensor:
     """Causal attention of every row over its request's pages, for any key and value widths.  A query row is the FP32
     part q_f32 [H*T or T*H rows, da] followed by q [rows, db] in the pages' dtype (either may be None); rows are head-major
     (h T + t) or token-major.  k_pages [Hkv, P, page, dk]; v_pages [Hkv, P, page, dv], possibly a view into k_pages (the
     last axis contiguous, the others with k's strides).  window: only the last `window` keys; chunk: only keys of the
     position's own block of `chunk` positions; talk FP32 [H, H]: the heads' softmax weights are mixed by it before the
     values; sinks FP32 [H]: exp(sinks[h]) joins head h's softmax denominator (it has no key and no value, is not scaled
-    and counts once).  Returns [H, T, dv] (out_head_major) or [T, H dv].
+    and counts once).  softcap > 0: a scaled score s becomes softcap * tanh(s / softcap).  maps > 1: every head attends
+    `maps` times, each time with queries and keys of its own, over the same values: H counts heads x maps query rows per
+    token (a head's maps side by side), k_pages holds groups x maps key heads (a group's maps side by side) and v_pages one
+    head per group; the result has one row per (head, map).  out_f32: the result leaves as FP32 whatever the pages hold.
+    Returns [H, T, dv] (out_head_major) or [T, H dv].
     tiles = (first row, token count, number) of row tiles of attention_flex_tile_tokens(H, Hkv) tokens of one request
     each, with max_context the largest position + 1 of the step: bfloat16 pages then go to the tensor-core kernel where
     it takes the shapes; with few tiles it splits the keys into fixed ranges and merges them."""
@@ -1201,7 +1228,10 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
         _need(q, "q", k_pages.dtype)
     Hkv, num_pages, page_size, dk = k_pages.shape
     dv = v_pages.shape[-1]
-    if da + db != dk or v_pages.dtype != k_pages.dtype or tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]):
+    if maps < 1 or Hkv % maps or (talk is not None and (maps > 1 or softcap or out_f32)):
+        raise KernelError(f"attention_flex: {maps} maps over {Hkv} key heads (mixed heads take one map, no cap, no FP32 result)")
+    if (da + db != dk or v_pages.dtype != k_pages.dtype or tuple(v_pages.shape[1:3]) != tuple(k_pages.shape[1:3])
+            or v_pages.shape[0] * maps != Hkv):
         raise KernelError(f"attention_flex: a query of {da}+{db} against pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)}")
     for nm, p in (("k_pages", k_pages), ("v_pages", v_pages)):
         if not p.is_cuda or p.stride(3) != 1 or p.stride(1) != page_size * p.stride(2):
@@ -1210,7 +1240,8 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
         _need(talk, "talk", torch.float32, (H, H))
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (H,))
-    out = torch.empty((H, T, dv) if out_head_major else (T, H * dv), dtype=k_pages.dtype, device=k_pages.device)
+    out = torch.empty((H, T, dv) if out_head_major else (T, H * dv), dtype=torch.float32 if out_f32 else k_pages.dtype, device=k_pages.device)
+    as_f32 = out if out_f32 and k_pages.dtype != torch.float32 else None      # FP32 pages: the kernel's own result type
     shared_v = v_pages.data_ptr() == k_pages.data_ptr() and v_pages.stride() == k_pages.stride()
     if (tiles is not None and k_pages.dtype == torch.bfloat16 and not (talk is not None and out_head_major)
             and attention_flex_mma_supported(H, Hkv, dk, dv, k_pages.stride(2), v_pages.stride(2), db, shared_v)):
@@ -1236,12 +1267,25 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
               _ll(k_pages.stride(0)), _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv),
               _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tok0), _ptr(ntok),
               _i(n_tiles), _i(window or 0), _i(chunk or 0), _f(scale), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv),
-              _i(nsplit), _i(split_keys), _ptr(ws), _ptr(talk), _ptr(sinks), _stream())
+              _i(nsplit), _i(split_keys), _ptr(ws), _ptr(talk), _ptr(sinks), _f(softcap), _i(maps), _ptr(as_f32), _stream())
         return out
     _call("q6k_attention_flex", _ptr(q_f32), _i(da), _ptr(q), _i(db), _i(1 if head_major else 0), _ptr(k_pages), _ll(k_pages.stride(0)),
           _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _i(chunk or 0), _f(scale),
-          _ptr(talk), _ptr(sinks), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv), _i(dtype_code(k_pages.dtype)), _stream())
+          _ptr(talk), _ptr(sinks), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv), _i(dtype_code(k_pages.dtype)),
+          _f(softcap), _i(maps), _ptr(as_f32), _stream())
+    return out
+
+
+def map_difference(a: torch.Tensor, H: int, dv: int, weight: float, eps: float, mult: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """The two maps of every head combined: a FP32 [T, H 2 dv] (a head's maps side by side) -> [T, H dv] in out_dtype,
+    o = a1 - weight a2, then o / sqrt(mean(o^2) + eps) * mult over each head's dv values."""
+    _need(a, "a", torch.float32)
+    T = a.shape[0]
+    if a.dim() != 2 or a.shape[1] != H * 2 * dv:
+        raise KernelError("map_difference: shapes disagree")
+    out = torch.empty((T, H * dv), dtype=out_dtype, device=a.device)
+    _call("q6k_map_difference", _ptr(a), _ptr(out), _i(T), _i(H), _i(dv), _f(weight), _f(eps), _f(mult), _i(dtype_code(out_dtype)), _stream())
     return out
 
 
@@ -1326,8 +1370,15 @@ def gated_delta(u: torch.Tensor, p: torch.Tensor, b_col: int, a_col: int, A_log:
     return o
 
 
-def delta_out(o: torch.Tensor, p: torch.Tensor, g_col: int, w: torch.Tensor, eps: float, H: int, dv: int, out_dtype: torch.dtype) -> torch.Tensor:
-    """out_dtype(o / rms(o) * w * silu(gate)) per (row, head): o FP32 [T, H dv], the gate in p's columns from g_col on."""
+OUT_GATES = {"silu": 0, "sigmoid": 1}
+
+
+def delta_out(o: torch.Tensor, p: torch.Tensor, g_col: int, w: torch.Tensor, eps: float, H: int, dv: int, out_dtype: torch.dtype,
+              gate: str = "silu") -> torch.Tensor:
+    """out_dtype(o / rms(o) * w * gate(g)) per (row, head): o FP32 [T, H dv], g in p's columns from g_col on; gate: silu or
+    sigmoid.  With H = 1 and dv the width of all heads together, the heads are normed as one vector."""
+    if gate not in OUT_GATES:
+        raise KernelError(f"delta_out: unknown gate {gate!r}; known: {', '.join(OUT_GATES)}")
     _need(o, "o", torch.float32)
     _need(p, "p", torch.float32)
     _need(w, "w", torch.float32, (dv,))
@@ -1336,7 +1387,7 @@ def delta_out(o: torch.Tensor, p: torch.Tensor, g_col: int, w: torch.Tensor, eps
         raise KernelError("delta_out: shapes disagree")
     out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
     _call("q6k_delta_out", _ptr(o), _ptr(p), _i(p.stride(0)), _i(g_col), _ptr(w), _f(eps), _ptr(out), _i(T), _i(H), _i(dv), _i(dtype_code(out_dtype)),
-          _stream())
+          _i(OUT_GATES[gate]), _stream())
     return out
 
 
@@ -1395,9 +1446,13 @@ def activate(x: torch.Tensor, I: int, gated: bool, act: str, out_dtype: torch.dt
     return out
 
 
-def route_biased(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], scale: float):
+def route_biased(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], scale: float, renorm: bool = True, groups=None):
     """(sel_e int32 [T, k], sel_w float32 [T, k]): per row the k experts with the largest sigmoid(logit) + bias (ties to the
-    lower index); weights sigmoid(logit) / (their sum + 1e-20) * scale.  logits: [T, E] or [slices, T, E] partial sums."""
+    lower index); weights sigmoid(logit) / (their sum + 1e-20) * scale, or sigmoid(logit) * scale without renorm.
+    groups = (count, keep): the experts form `count` equal groups of neighbours, a group's worth is the sum of its two
+    largest choice values, and only experts of the `keep` groups of most worth can be chosen.
+    logits: [T, E] or [slices, T, E] partial sums."""
+    count, keep = groups if groups is not None else (1, 1)
     _need(logits, "logits", torch.float32)
     slices = logits.shape[0] if logits.dim() == 3 else 1
     T, E = logits.shape[-2:]
@@ -1405,7 +1460,8 @@ def route_biased(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], sca
         _need(bias, "bias", torch.float32, (E,))
     sel_e = torch.empty((T, k), dtype=torch.int32, device=logits.device)
     sel_w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
-    _call("q6k_route_biased", _ptr(logits), _i(slices), _ptr(bias), _f(scale), _i(T), _i(E), _i(k), _ptr(sel_e), _ptr(sel_w), _stream())
+    _call("q6k_route_biased", _ptr(logits), _i(slices), _ptr(bias), _f(scale), _i(T), _i(E), _i(k), _ptr(sel_e), _ptr(sel_w),
+          _i(1 if renorm else 0), _i(count), _i(keep), _stream())
     return sel_e, sel_w
 
 
@@ -1466,15 +1522,17 @@ def retention_max_dim() -> int:
     return lib.q6k_retention_max_dim()
 
 
-def retention_prep(p: torch.Tensor, H: int, dk: int, q_col: int, k_col: int, rotary, k_scale: float, positions: torch.Tensor) -> None:
-    """In place on p FP32 [T, N]: the first rotary_dim entries of every head of q (columns q_col...) and k (k_col...)
-    turn by position * inv_freq[pair]; k is then multiplied by k_scale.  rotary = (inv_freq, rotary_dim, neighbours) or None."""
+def retention_prep(p: torch.Tensor, H: int, dk: int, q_col: int, k_col: int, rotary, k_scale: float, positions: torch.Tensor,
+                   act_cols: int = 0) -> None:
+    """In place on p FP32 [T, N]: the row's first act_cols columns pass through silu; then the first rotary_dim entries of
+    every head of q (columns q_col...) and k (k_col...) turn by position * inv_freq[pair]; k is then multiplied by k_scale.
+    rotary = (inv_freq, rotary_dim, neighbours) or None."""
     _need(p, "p", torch.float32)
     inv_freq, rd, neighbours = rotary if rotary is not None else (None, 0, False)
     if p.dim() != 2 or max(q_col, k_col) + H * dk > p.shape[1]:
         raise KernelError("retention_prep: shapes disagree")
     _call("q6k_retention_prep", _ptr(p), _i(p.stride(0)), _i(p.shape[0]), _i(H), _i(dk), _i(q_col), _i(k_col), _ptr(inv_freq), _i(rd),
-          _i(1 if neighbours else 0), _f(k_scale), _ptr(positions), _stream())
+          _i(1 if neighbours else 0), _f(k_scale), _ptr(positions), _i(act_cols), _stream())
 
 
 def retention(p: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,

@@ -20,6 +20,7 @@ under a name with the matching `register_*`; a spec.PartSpec(kind=name, params=.
                   float32 [T, D] result (or [slices, T, D] partial sums) for the block's next norm to add
   FeedForward     tensors(); bind(); forward(xn [T, D], ctx, out_f32 [T, D]) adds its result into `out`
   Block           built from (norm1, mixer, norm2, ffn); forward(h, ctx, cache, state)
+  EmbedAdd        tensors(); bind(); state_shape() as a mixer's; forward(h_f32 [T, D], ctx, state) adds into h in place
 """
 from __future__ import annotations
 
@@ -55,9 +56,11 @@ class CacheRequest:
     v_dim: Optional[int] = None         # width of a value; None: the key's
     dtype: Optional[torch.dtype] = None  # what the pages hold; None: the runtime's operand dtype
     values_in_keys: bool = False        # a value is the first v_dim entries of its key row (a cached latent): no pages of its own
+    v_heads: Optional[int] = None       # heads of the value pages; None: kv_heads (several key heads may share one value head)
 
     def key(self) -> Tuple:
-        return (self.kind, self.window, self.kv_heads, self.head_dim, self.v_dim or self.head_dim, self.dtype, self.values_in_keys)
+        return (self.kind, self.window, self.kv_heads, self.head_dim, self.v_dim or self.head_dim, self.dtype, self.values_in_keys,
+                self.v_heads or self.kv_heads)
 
 
 @dataclass
@@ -203,6 +206,17 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class EmbedAdd(Part):
+    """Something added to the embedding output before the first layer.  state_shape() as a mixer's (per-request state in
+    the request's slot, zeroed when the slot is handed out); forward(h, ctx, state) adds into the FP32 stream h in place."""
+
+    def state_shape(self):
+        return None
+
+    def forward(self, h, ctx, state) -> None:
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     defers_add = False                    # forward(..., defer=True) may return a WeightedRows instead of adding
 
@@ -236,6 +250,7 @@ POSITION_ENCODINGS: Dict[str, type] = {}
 MIXERS: Dict[str, type] = {}
 FEED_FORWARDS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
+EMBED_ADDS: Dict[str, type] = {}
 
 
 def _register(table: Dict[str, type], what: str):
@@ -252,6 +267,7 @@ register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_mixer = _register(MIXERS, "mixer")
 register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_block = _register(BLOCKS, "block")
+register_embed_add = _register(EMBED_ADDS, "embedding add")
 
 
 def make_part(table: Dict[str, type], what: str, spec: PartSpec, **extra):

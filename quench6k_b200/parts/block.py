@@ -47,7 +47,8 @@ class SandwichBlock(Block):
 @register_block("parallel")
 class ParallelBlock(Block):
     """Mixer and feed-forward side by side, each behind a norm of its own, both reading the same stream:
-    h += scale * (mixer(norm1(h)) + ffn(norm2(h))); a block without a feed-forward adds the mixer alone.  The add is left
+    h += scale * (mixer(norm1(h)) + ffn(norm2(h))); a block without a feed-forward adds the mixer alone.  A block built
+    without a second norm although it has a feed-forward gives both sublayers the first norm's output.  The add is left
     to the next block (or the model's last norm); with RMS norms of one eps, one kernel makes the add the block before has
     left and both norms in one pass over the row."""
 
@@ -72,6 +73,8 @@ class ParallelBlock(Block):
                 pending.apply(h)
             x1 = n1.forward(h)
             x2 = n2.forward(h) if n2 is not None else None
+        if n2 is None:
+            x2 = x1                                       # one norm for both sublayers
         ctx.hold_results = self.ffn is not None           # the mixer's result waits while the feed-forward runs
         y = self.mixer.forward(x1, ctx, cache, state, None)
         ctx.hold_results = False
@@ -81,6 +84,9 @@ class ParallelBlock(Block):
             return ScaledSum(self.scale, y)
         if hasattr(self.ffn, "compute") and not getattr(self.ffn, "defers_add", False):
             return ScaledSum(self.scale, y, self.ffn.compute(x2, ctx))
+        if self.ffn.defers_add and getattr(self.ffn, "shared", None) is not None and hasattr(self.ffn, "compute"):
+            both, rows = self.ffn.compute(x2, ctx)        # what every token shares (possibly split-K slices) and the routed rows, unsummed
+            return ScaledSum(self.scale, y, both, rows)
         if self.ffn.defers_add:
             acc = None
             rows = self.ffn.forward(x2, ctx, None, defer=True) if getattr(self.ffn, "always_defers", False) else None

@@ -71,19 +71,25 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int, scoring: str = "softmax",
                  renormalize: bool = True, shared_intermediate_size: int = 0, gated: bool = True, act: str = "silu",
                  correction: bool = False, route_scale: float = 1.0, names=None, shared_act=None, shared_prefix: str = "shared_experts.",
-                 shared_names=None):
+                 shared_names=None, groups=None):
         """gated: an expert is down(act(gate x) * (up x)); else down(act(up x)).  correction: a stored vector added to the
         scores for the choice of the experts only (the weights use the scores without it); route_scale multiplies the
-        weights.  Both belong to sigmoid scoring with renormalised weights.  act may be a gate with its constant, such as
+        weights.  groups = (count, keep): the experts form `count` equal groups of neighbours, and only experts of the `keep`
+        groups whose two largest choice values add up to most can be chosen.  All three belong to sigmoid scoring (with
+        renormalised weights, or with the plain scores as weights).  act may be a gate with its constant, such as
         ("clamped", limit) (gated experts only).  The shared expert has the experts' form with an activation (shared_act,
         default the experts'), a tensor prefix and tensor names of its own."""
         act = _checked_act(act)
         if isinstance(act, tuple) and not gated:
             raise ValueError(f"the gate {act[0]!r} belongs to gated experts")
         self.gated, self.act, self.has_correction, self.route_scale = bool(gated), act, bool(correction), float(route_scale)
-        self.own_router = self.has_correction or self.route_scale != 1.0
-        if self.own_router and not (scoring == "sigmoid" and renormalize):
-            raise ValueError("a correction of the choice and a scale of the weights go with sigmoid scores and renormalised weights")
+        self.groups = (int(groups[0]), int(groups[1])) if groups is not None and int(groups[0]) > 1 else None
+        if self.groups is not None and (num_experts % self.groups[0] or not 0 < self.groups[1] <= self.groups[0]
+                                        or top_k > self.groups[1] * (num_experts // self.groups[0])):
+            raise ValueError(f"{num_experts} experts in {self.groups[0]} groups of which {self.groups[1]} are kept, {top_k} chosen")
+        self.own_router = self.has_correction or self.route_scale != 1.0 or self.groups is not None
+        if self.own_router and scoring != "sigmoid":
+            raise ValueError("a correction of the choice, groups of experts and a scale of the weights go with sigmoid scores")
         self.names = {"router": "gate.weight", "gate": "experts.gate_proj.weight", "up": "experts.up_proj.weight",
                       "down": "experts.down_proj.weight", "correction": "gate.correction", **(names or {})}
         if scoring not in ("softmax", "sigmoid"):
@@ -174,7 +180,7 @@ class RoutedExperts(FeedForward):
         ops.current_tag = "experts.router"
         logits = linear.matmul(xn, self.w_router, rt, partials_ok=True)    # FP32 [T, E], or split-K slices of it that route() sums
         if self.own_router:
-            sel_e, sel_w = ops.route_biased(logits, self.k, self.correction, self.route_scale)
+            sel_e, sel_w = ops.route_biased(logits, self.k, self.correction, self.route_scale, renorm=self.renorm, groups=self.groups)
         else:
             sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         if self.routing_tap is not None:

@@ -28,6 +28,7 @@ class LayerSpec:
     post_norm: Optional[PartSpec] = None    # the kind of the norms on the sublayers' results, in arrangements that have them
     block_params: Dict[str, Any] = field(default_factory=dict)   # constants of the arrangement (a multiplier on what it adds, ...)
     side: Optional[PartSpec] = None         # a third sublayer fed by the model's side table (arrangements that have one)
+    shared_norm: bool = False               # the feed-forward reads the first norm's output: the block has no second norm
 
 
 @dataclass
@@ -57,6 +58,10 @@ class ModelSpec:
     # a second embedding table (name, columns): the step gathers the tokens' rows of it once, FP32, and layers read their
     # columns of them (StepContext.side_rows)
     side_table: Optional[Tuple[str, int]] = None
+    # what is added to the embedding output before the first layer (a key of parts.EMBED_ADDS), e.g. a table indexed by a
+    # hash of the token and the one before it; its tensors' names follow embed_add_prefix
+    embed_add: Optional[PartSpec] = None
+    embed_add_prefix: str = "model.embed_add."
 
 
 @dataclass

@@ -394,7 +394,28 @@ def sigusun_config(size):
             "layers": layers}
 
 
+def kitodra_config(size):
+    """Kitodra at layer sizes that resemble a real model's: a lightning layer, a window layer whose values are its keys,
+    a difference attention layer inside chunks (two maps of half a head's width) and another lightning layer, each with
+    clamped routed experts chosen among the best groups and a shared expert; the four run twice, the second time as layers
+    that use the first four's tensors (own caches and states); the token-pair table on the embedding."""
+    D, heads, kv, E, top, eff, window = {"s": (1024, 8, 2, 32, 4, 512, 1024), "m": (2048, 16, 4, 64, 4, 1024, 2048)}[size]
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": E, "top": top, "groups": {"count": 8, "keep": 4}},
+           "shared": {"ff": eff, "limit": 7.0}}
+    light = {"type": "lightning", "mlp": moe,
+             "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / heads) for h in range(heads)]}}
+    win = {"type": "attention_2", "mlp": moe, "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                                         "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 64}}}
+    diff = {"type": "attention", "mlp": moe, "mixer": {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 30.0,
+                                                        "diff": 0.5, "mask": {"size": window}}}
+    layers = [light, win, diff, dict(light)]
+    layers += [dict(L, weights_of=i) for i, L in enumerate(layers)]
+    return {"architecture": "Kitodra", "vocab": 32768, "width": D, "norm": {"eps": 1e-6}, "kv_page_size": 16,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
+
+
 DESIGNS = {"pedotar": (("pedotar", pedotar_config), ("flint_dense", flint_dense_config)),
+           "kitodra": (("kitodra", kitodra_config), ("sigusun", sigusun_config), ("kipedra", kipedra_config)),
            "kipedra": (("kipedra", kipedra_config), ("flint_routed", flint_routed_config)),
            "sigusun": (("sigusun", sigusun_config), ("kipedra", kipedra_config), ("pedotar", pedotar_config))}
 
@@ -559,9 +580,9 @@ def main():
     ap.add_argument("--profile-ops", action="store_true",
                     help="instead of the benchmark line: where an eager decode step and a prefill step spend their time, launcher by "
                          "launcher (CUDA events around every launch; its own JSON line)")
-    ap.add_argument("--design", default=None, choices=["pedotar", "kipedra", "sigusun"],
+    ap.add_argument("--design", default=None, choices=["pedotar", "kipedra", "sigusun", "kitodra"],
                     help="instead of the benchmark line: prefill and decode throughput of that design beside the closest Flint model "
-                         "(pedotar: dense feed-forwards; kipedra: windows and routed experts; sigusun: beside Kipedra and Pedotar) at equal layer sizes (--sizes), with each "
+                         "(pedotar: dense feed-forwards; kipedra: windows and routed experts; sigusun: beside Kipedra and Pedotar; kitodra: beside Sigusun and Kipedra) at equal layer sizes (--sizes), with each "
                          "model's time launcher by launcher (its own JSON line)")
     ap.add_argument("--sizes", default="s,m", help="--design: s (width 1024) and/or m (width 2048)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gated_delta", "retention"],

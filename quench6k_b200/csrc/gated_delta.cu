@@ -400,6 +400,36 @@ __global__ void __launch_bounds__(128) delta_out_kernel(const float* o, const fl
     for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(orow[i] * inv * w[i] * gate_f(grow[i], gate));
 }
 
+// The same for ONE wide head (all heads' values normed together): a block per token, the row's values kept in registers
+// between the sum of squares and the products (up to 16 a thread), read again beyond that.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_out_row_kernel(const float* o, const float* p, int ldp, int g_col, const float* w, float eps, T* out,
+                                                            int N, int gate) {
+    pdl_enter();
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const float* orow = o + (size_t)t * N;
+    const float* grow = p + (size_t)t * ldp + g_col;
+    T* dst = out + (size_t)t * N;
+    constexpr int PER = 16;
+    float v[PER];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        v[j] = i < N ? orow[i] : 0.0f;
+        ss = fmaf(v[j], v[j], ss);
+    }
+    for (int i = threadIdx.x + 256 * PER; i < N; i += 256) ss = fmaf(orow[i], orow[i], ss);
+    const float inv = rsqrtf(block_sum(ss, red) / (float)N + eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < N) dst[i] = from_f32<T>(v[j] * inv * w[i] * gate_f(grow[i], gate));
+    }
+    for (int i = threadIdx.x + 256 * PER; i < N; i += 256) dst[i] = from_f32<T>(orow[i] * inv * w[i] * gate_f(grow[i], gate));
+}
+
 }  // namespace
 
 // out[t, c] = act(short convolution of the projected channel c up to row t) for c < C; columns C..copy_to of x are
@@ -467,6 +497,10 @@ Q6K_API int q6k_delta_out(const float* o, const float* p, int ldp, int g_col, co
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && H > 0 && dv > 0 && (gate == 0 || gate == 1), "delta_out: bad sizes T=%d H=%d dv=%d gate=%d", T_, H, dv, gate);
     Q6K_REQUIRE((H + 3) / 4 <= 65535, "delta_out: %d heads exceed the grid limit", H);
+    if (H == 1 && dv > 256) {                 // one wide head: a block per token
+        Q6K_DISPATCH(dtype, q6k_launch(delta_out_row_kernel<T>, dim3(T_), 256, 0, st, o, p, ldp, g_col, w, eps, (T*)out, dv, gate););
+        return q6k_check_launch("delta_out");
+    }
     Q6K_DISPATCH(dtype, q6k_launch(delta_out_kernel<T>, dim3(T_, (H + 3) / 4), 128, 0, st, o, p, ldp, g_col, w, eps, (T*)out, H, dv, gate););
     return q6k_check_launch("delta_out");
 }

@@ -92,9 +92,10 @@ def difference_attention(h, w, m, eps):
     return out.reshape(T, H * dv) @ w("o").T + w("o.b")
 
 
-def sink_attention(h, w, m, eps):
+def sink_attention(h, w, m, eps, sink=True):
     """Softmax attention in a sliding window whose denominator holds one more term of score zero; the values are the
-    projected keys (before rotation and norm); q and k are rotated over their first dims entries, then divided by their root mean square."""
+    projected keys (before rotation and norm); q and k are rotated over their first dims entries, then divided by their root
+    mean square.  sink=False leaves the extra term out (for tests that ask whether it would show)."""
     T = h.shape[0]
     H, G, d, win = m["heads"], m["kv_heads"], m["dim"], m["mask"]["size"]
     pos = torch.arange(T)
@@ -111,7 +112,7 @@ def sink_attention(h, w, m, eps):
             s = (k[lo:i + 1, g] @ q[i, head]) * m["scale"]
             top = torch.clamp(s.max(), min=0.0)
             e = torch.exp(s - top)
-            out[i, head] = (e / (e.sum() + torch.exp(-top))) @ v[lo:i + 1, g]
+            out[i, head] = (e / (e.sum() + (torch.exp(-top) if sink else 0.0))) @ v[lo:i + 1, g]
     return out.reshape(T, -1) @ w("o").T + w("o.b")
 
 
@@ -174,9 +175,10 @@ def weights_layer(cfg, i):
     return i
 
 
-def forward(cfg, weights, tokens, forced=None, layers_out=None):
+def forward(cfg, weights, tokens, forced=None, layers_out=None, mixers=None):
     """Logits [T, vocab] of one sequence.  forced: {layer: [T, top]} experts to use in place of the router's choice.
-    forward.chosen holds the experts each routed layer chose.  layers_out: a list that receives the stream after every layer."""
+    forward.chosen holds the experts each routed layer chose.  layers_out: a list that receives the stream after every layer.
+    mixers: other functions for some mixer types (tests that break a mechanism on purpose)."""
     W = {k: v.to(F) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
     tok = torch.as_tensor(tokens, dtype=torch.long)
@@ -188,7 +190,7 @@ def forward(cfg, weights, tokens, forced=None, layers_out=None):
     for i, L in enumerate(cfg["layers"]):
         j = weights_layer(cfg, i)
         h = rms_norm(x, W[f"l{j}.norm1"], eps)
-        y = MIXERS[L["type"]](h, lambda n, j=j: W[f"l{j}.mix.{n}"], L["mixer"], eps)
+        y = {**MIXERS, **(mixers or {})}[L["type"]](h, lambda n, j=j: W[f"l{j}.mix.{n}"], L["mixer"], eps)
         if L.get("mlp") is not None:
             f, forward.chosen[i] = routed_experts(h, lambda n, j=j: W[f"l{j}.mlp.{n}"], L["mlp"], None if forced is None else forced.get(i))
             y = y + f

@@ -1,7 +1,7 @@
 // The closing add of a block whose sublayers run side by side, and the norms that open the next block, in one pass over
 // the row:
 //
-//   h[t] += m * (a[t] + b[t] + sum_s pw[t, s] * py[row(t, s)])          (each of the three optional)
+//   h[t] += m * (a[t] + bias + b[t] + sum_s pw[t, s] * py[row(t, s)])   (each of the four optional; bias: one vector for all rows)
 //   out1[r] = T(h[t] * rsqrt(mean(h[t]^2) + eps) * w1),  out2[r] likewise with w2    (each optional; t = rows[r] or r)
 //
 // a and b may be split-K partial sums [slices, T, D], added in order.  Everything is FP32; the outputs are in the
@@ -14,12 +14,12 @@ template <typename T>
 __global__ void __launch_bounds__(256) scaled_add_norm_kernel(float* h, const float* a, int a_slices, const float* b, int b_slices, size_t slice_stride,
                                                               const float* py, const int* pair_row, const float* pw, int S, float m,
                                                               const int* rows, const float* w1, T* out1, const float* w2, T* out2, float eps,
-                                                              int D) {
+                                                              int D, const float* bias) {
     pdl_enter();
     __shared__ float red[32];
     const int r = blockIdx.x, t = rows ? rows[r] : r;
     float* hr = h + (size_t)t * D;
-    const bool adds = a || b || py;
+    const bool adds = a || b || py || bias;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float v = hr[i];
@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(256) scaled_add_norm_kernel(float* h, const fl
                 sum = a[(size_t)t * D + i];
                 for (int s = 1; s < a_slices; ++s) sum += a[s * slice_stride + (size_t)t * D + i];
             }
+            if (bias) sum += bias[i];
             if (b) {
                 float sb = b[(size_t)t * D + i];
                 for (int s = 1; s < b_slices; ++s) sb += b[s * slice_stride + (size_t)t * D + i];
@@ -62,12 +63,12 @@ template <typename T>
 __global__ void __launch_bounds__(256) scaled_add_norm4_kernel(float* h, const float* a, int a_slices, const float* b, int b_slices, size_t slice_stride,
                                                                const float* py, const int* pair_row, const float* pw, int S, float m,
                                                                const int* rows, const float* w1, T* out1, const float* w2, T* out2, float eps,
-                                                               int D) {
+                                                               int D, const float* bias) {
     pdl_enter();
     __shared__ float red[32];
     const int r = blockIdx.x, t = rows ? rows[r] : r, D4 = D >> 2;
     float4* hr = reinterpret_cast<float4*>(h + (size_t)t * D);
-    const bool adds = a || b || py;
+    const bool adds = a || b || py || bias;
     float4 keep[4];
     float ss = 0.0f;
 #pragma unroll
@@ -81,6 +82,7 @@ __global__ void __launch_bounds__(256) scaled_add_norm4_kernel(float* h, const f
                 sum = reinterpret_cast<const float4*>(a + (size_t)t * D)[i];
                 for (int s = 1; s < a_slices; ++s) add4(sum, reinterpret_cast<const float4*>(a + s * slice_stride + (size_t)t * D)[i]);
             }
+            if (bias) add4(sum, reinterpret_cast<const float4*>(bias)[i]);
             if (b) {
                 float4 sb = reinterpret_cast<const float4*>(b + (size_t)t * D)[i];
                 for (int s = 1; s < b_slices; ++s) add4(sb, reinterpret_cast<const float4*>(b + s * slice_stride + (size_t)t * D)[i]);
@@ -236,22 +238,22 @@ __global__ void route_biased_kernel(const float* logits, int slices, size_t slic
 
 Q6K_API int q6k_scaled_add_norm(float* h, const float* a, int a_slices, const float* b, int b_slices, long long slice_stride, const float* py,
                                 const int* pair_row, const float* pw, int S, float m, const int* rows, const float* w1, void* out1,
-                                const float* w2, void* out2, float eps, int R, int D, int dtype, cudaStream_t st) {
+                                const float* w2, void* out2, float eps, int R, int D, int dtype, const float* bias, cudaStream_t st) {
     if (R == 0) return 0;
     Q6K_REQUIRE(R > 0 && D > 0 && a_slices >= 1 && b_slices >= 1, "scaled_add_norm: bad sizes R=%d D=%d", R, D);
-    Q6K_REQUIRE(!(rows && (a || b || py)), "scaled_add_norm: the add takes no row selection");
+    Q6K_REQUIRE(!(rows && (a || b || py || bias)), "scaled_add_norm: the add takes no row selection");
     Q6K_REQUIRE(!py || (pw && S > 0), "scaled_add_norm: weighted rows need their weights");
     Q6K_REQUIRE((out1 == nullptr || w1) && (out2 == nullptr || w2), "scaled_add_norm: an output needs its weight");
     auto on16 = [](const void* ptr) { return ((uintptr_t)ptr & 15) == 0; };
-    const bool vec = D % 4 == 0 && D <= 4096 && slice_stride % 4 == 0 && on16(h) && on16(a) && on16(b) && on16(py) && on16(w1) && on16(w2);
+    const bool vec = D % 4 == 0 && D <= 4096 && slice_stride % 4 == 0 && on16(h) && on16(a) && on16(b) && on16(py) && on16(w1) && on16(w2) && on16(bias);
     // which of the two kernels runs depends on the row width and the buffers' alignment alone, never on the step
     if (vec) {
         Q6K_DISPATCH(dtype, q6k_launch(scaled_add_norm4_kernel<T>, R, 256, 0, st, h, a, a_slices, b, b_slices, (size_t)slice_stride, py, pair_row, pw, S, m,
-                                       rows, w1, (T*)out1, w2, (T*)out2, eps, D););
+                                       rows, w1, (T*)out1, w2, (T*)out2, eps, D, bias););
         return q6k_check_launch("scaled_add_norm");
     }
     Q6K_DISPATCH(dtype, q6k_launch(scaled_add_norm_kernel<T>, R, 256, 0, st, h, a, a_slices, b, b_slices, (size_t)slice_stride, py, pair_row, pw, S, m,
-                                   rows, w1, (T*)out1, w2, (T*)out2, eps, D););
+                                   rows, w1, (T*)out1, w2, (T*)out2, eps, D, bias););
     return q6k_check_launch("scaled_add_norm");
 }
 

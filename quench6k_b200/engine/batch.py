@@ -47,6 +47,9 @@ class StepContext:
     fed: Optional[torch.Tensor] = None            # int32 ids the step before sampled: a token id -(i + 1) stands for fed[i]
     hold_results: bool = False                    # a block that keeps a sublayer's result while other kernels run sets it: results
                                                   # must then be tensors of their own, not views of the products' scratch buffer
+    leave_bias: bool = False                      # a block that adds a per-column bias with the sublayer's result sets it: a mixer whose
+                                                  # last projection has a bias then hands the bias over in `left_bias` instead of adding it
+    left_bias: Optional[torch.Tensor] = None
     position: int = 0                             # the executed position (index into the model's order) whose block is running
     side_rows: Optional[torch.Tensor] = None      # FP32 [T, columns]: the tokens' rows of the model's side table, if it has one
 

@@ -1393,9 +1393,10 @@ def delta_out(o: torch.Tensor, p: torch.Tensor, g_col: int, w: torch.Tensor, eps
 
 # --------------------------------------------------------------------------- a block of sublayers side by side
 def scaled_add_norm(h: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], weighted, scale: float, w1: Optional[torch.Tensor],
-                    w2: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
-    """h += scale * (a + b + weighted rows) in place (each optional; a and b FP32 [T, D] or [slices, T, D] partial sums, weighted =
-    (y, pair_row, weights) as in `combine`), then (out1, out2) = h * rsqrt(mean(h^2) + eps) * (w1, w2) in out_dtype for the
+                    w2: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                    bias: Optional[torch.Tensor] = None):
+    """h += scale * (a + bias + b + weighted rows) in place (each optional; a and b FP32 [T, D] or [slices, T, D] partial sums,
+    bias FP32 [D] the same for every row, weighted = (y, pair_row, weights) as in `combine`), then (out1, out2) = h * rsqrt(mean(h^2) + eps) * (w1, w2) in out_dtype for the
     weights given (None otherwise).  rows: normalise these rows only (no add then)."""
     _need(h, "h", torch.float32)
     T, D = h.shape
@@ -1430,8 +1431,10 @@ def scaled_add_norm(h: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torc
             outs.append(None)
     if rows is not None:
         _need(rows, "rows", torch.int32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (D,))
     _call("q6k_scaled_add_norm", _ptr(h), _ptr(a), _i(counts[0]), _ptr(b), _i(counts[1]), _ll(stride), _ptr(y), _ptr(pair_row), _ptr(pair_w), _i(S),
-          _f(scale), _ptr(rows), _ptr(w1), _ptr(outs[0]), _ptr(w2), _ptr(outs[1]), _f(eps), _i(R), _i(D), _i(dtype_code(out_dtype)), _stream())
+          _f(scale), _ptr(rows), _ptr(w1), _ptr(outs[0]), _ptr(w2), _ptr(outs[1]), _f(eps), _i(R), _i(D), _i(dtype_code(out_dtype)), _ptr(bias), _stream())
     return outs[0], outs[1]
 
 

@@ -193,7 +193,9 @@ class Attention(Mixer):
     def _out(self, a, ctx):
         """The output projection (FP32, possibly split-K slices) and its bias."""
         rt = self.rt
-        if not self.has_o_bias:
+        if not self.has_o_bias or ctx.leave_bias:
+            if self.has_o_bias:
+                ctx.left_bias = self.o_bias                       # the block adds it together with the result
             return linear.matmul(a, self.w_o, rt, partials_ok=not ctx.hold_results)
         y = linear.matmul(a, self.w_o, rt, partials_ok=True)
         ops.current_tag = "attention.o_bias"                      # the slices summed and the bias added: one tap of weight one

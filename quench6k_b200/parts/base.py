@@ -125,18 +125,20 @@ class PostNormed:
 
 @dataclass
 class ScaledSum:
-    """A residual add that has not been made yet: h += scale * (a + b + weighted rows), what a block whose sublayers run
-    side by side leaves to the norms that open the next block (or to the model's last norm).  a, b: FP32 [T, D] or
-    [slices, T, D] partial sums to be added in order, or None."""
+    """A residual add that has not been made yet: h += scale * (a + bias + b + weighted rows), what a block whose sublayers
+    run side by side leaves to the norms that open the next block (or to the model's last norm).  a, b: FP32 [T, D] or
+    [slices, T, D] partial sums to be added in order, or None; bias: FP32 [D], the same for every row (a projection's), or None."""
     scale: float
     a: Optional[torch.Tensor] = None
     b: Optional[torch.Tensor] = None
     weighted: Optional[WeightedRows] = None
+    bias: Optional[torch.Tensor] = None
 
     def apply(self, h: torch.Tensor) -> None:
         from .. import ops
         w = self.weighted
-        ops.scaled_add_norm(h, self.a, self.b, None if w is None else (w.y, w.pair_row, w.weights), self.scale, None, None, 0.0, torch.float32)
+        ops.scaled_add_norm(h, self.a, self.b, None if w is None else (w.y, w.pair_row, w.weights), self.scale, None, None, 0.0, torch.float32,
+                            bias=self.bias)
 
 
 class Tap:

@@ -67,7 +67,7 @@ class ParallelBlock(Block):
             p = pending or ScaledSum(0.0)
             w = p.weighted
             x1, x2 = ops.scaled_add_norm(h, p.a, p.b, None if w is None else (w.y, w.pair_row, w.weights), p.scale, n1.weight,
-                                         n2.weight if n2 is not None else None, n1.eps, n1.rt.dtype)
+                                         n2.weight if n2 is not None else None, n1.eps, n1.rt.dtype, bias=p.bias)
         else:
             if pending is not None:
                 pending.apply(h)
@@ -76,27 +76,30 @@ class ParallelBlock(Block):
         if n2 is None:
             x2 = x1                                       # one norm for both sublayers
         ctx.hold_results = self.ffn is not None           # the mixer's result waits while the feed-forward runs
+        ctx.leave_bias = True                             # a mixer whose last projection has a bias may leave it to the add
+        ctx.left_bias = None
         y = self.mixer.forward(x1, ctx, cache, state, None)
-        ctx.hold_results = False
+        ctx.hold_results = ctx.leave_bias = False
+        bias = ctx.left_bias
         if y is None:
             raise TypeError(f"{type(self.mixer).__name__} adds into the stream itself; this arrangement needs its result")
         if self.ffn is None:
-            return ScaledSum(self.scale, y)
+            return ScaledSum(self.scale, y, bias=bias)
         if hasattr(self.ffn, "compute") and not getattr(self.ffn, "defers_add", False):
-            return ScaledSum(self.scale, y, self.ffn.compute(x2, ctx))
+            return ScaledSum(self.scale, y, self.ffn.compute(x2, ctx), bias=bias)
         if self.ffn.defers_add and getattr(self.ffn, "shared", None) is not None and hasattr(self.ffn, "compute"):
             both, rows = self.ffn.compute(x2, ctx)        # what every token shares (possibly split-K slices) and the routed rows, unsummed
-            return ScaledSum(self.scale, y, both, rows)
+            return ScaledSum(self.scale, y, both, rows, bias=bias)
         if self.ffn.defers_add:
             acc = None
             rows = self.ffn.forward(x2, ctx, None, defer=True) if getattr(self.ffn, "always_defers", False) else None
             if rows is None:
                 acc = h.new_zeros(h.shape)
                 rows = self.ffn.forward(x2, ctx, acc, defer=True)
-            return ScaledSum(self.scale, y, acc, rows)
+            return ScaledSum(self.scale, y, acc, rows, bias=bias)
         acc = h.new_zeros(h.shape)
         self.ffn.forward(x2, ctx, acc)
-        return ScaledSum(self.scale, y, acc)
+        return ScaledSum(self.scale, y, acc, bias=bias)
 
 
 @register_block("outnorm")

@@ -311,6 +311,81 @@ __global__ void __launch_bounds__(128) qkv_pages_kernel(const float* qkv, int ld
     for (int d = threadIdx.x; d < n; d += blockDim.x) dst[d] = from_f32<T>(turns ? rotated(xs, d, rd, neighbours, pos, inv_freq) : xs[d]);
 }
 
+// The same with a warp per (token, head), eight heads a block, for heads of at most 256 entries: a lane keeps its entries
+// (lane, lane + 32, ...) in registers, the head passes through the warp's stretch of shared memory once for the rotation's
+// partners, and the sums of squares are a warp's shuffles.  Same arithmetic and order of sums per head as the block kernel
+// has for one warp's share; which of the two runs depends on the head widths alone.
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_pages_warp_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, int hd, int vd,
+                                                             const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rd,
+                                                             int neighbours, const int* positions, const int* req_of_token,
+                                                             const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out,
+                                                             T* k_pages, T* v_pages, int heads) {
+    pdl_enter();
+    __shared__ float stage[8][256];
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * 8 + warp;
+    if (h >= heads) return;
+    const int kind = h < Hq ? 0 : h < Hq + Hkv ? 1 : 2;
+    const int pos = positions[t];
+    const int n = kind == 2 ? vd : hd;
+    const size_t col = kind == 0 ? (size_t)h * hd : kind == 1 ? (size_t)Hq * hd + (size_t)(h - Hq) * hd
+                                                              : (size_t)(Hq + Hkv) * hd + (size_t)(h - Hq - Hkv) * vd;
+    const float* src = qkv + (size_t)t * ld + col;
+    float x[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d = lane + 32 * j;
+        float v = 0.0f;
+        if (d < n) {
+            v = src[d];
+            for (int s = 1; s < splits; ++s) v += src[s * split_stride + d];
+        }
+        x[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float* nw = kind == 0 ? q_norm : kind == 1 ? k_norm : nullptr;
+    if (nw) {
+        const float inv = rsqrtf(warp_sum(ss) / (float)n + eps);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int d = lane + 32 * j;
+            if (d < n) x[j] = x[j] * inv * nw[d];
+        }
+    }
+    T* dst;
+    if (kind == 0) {
+        dst = q_out + ((size_t)t * Hq + h) * hd;
+    } else {
+        const int page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
+        if (page < 0) return;
+        const int kh = kind == 1 ? h - Hq : h - Hq - Hkv;
+        dst = (kind == 1 ? k_pages : v_pages) + (((size_t)kh * num_pages + page) * page_size + pos % page_size) * n;
+    }
+    const bool turns = inv_freq && kind != 2 && rd > 0;
+    if (turns) {
+        float* xs = stage[warp];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int d = lane + 32 * j;
+            if (d < n) xs[d] = x[j];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int d = lane + 32 * j;
+            if (d < n) dst[d] = from_f32<T>(rotated(xs, d, rd, neighbours, pos, inv_freq));
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d = lane + 32 * j;
+        if (d < n) dst[d] = from_f32<T>(x[j]);
+    }
+}
+
 // The inputs of attention over a cached latent.  x: FP32 [T, ld] = [H query heads of (dim + rd) | latent of `rank` | rd].
 // Block (t, h < H): the head's first `dim` values -> qn[(h T + t) dim] (they go through the key up-projection next), its
 // last rd values, the first `turn` of them rotated -> qr[(h T + t) rd].  Block (t, H): the latent, RMS-normed with weight
@@ -440,6 +515,12 @@ Q6K_API int q6k_qkv_pages(const float* qkv, int ld, int splits, long long split_
     Q6K_REQUIRE(heads <= 65535, "qkv_pages: %d heads exceed the grid limit", heads);
     const size_t smem = (size_t)(hd > vd ? hd : vd) * sizeof(float);
     Q6K_REQUIRE(smem <= 48 * 1024, "qkv_pages: heads of %d do not fit shared memory", hd > vd ? hd : vd);
+    if (hd <= 256 && vd <= 256 && (heads + 7) / 8 <= 65535) {                 // narrow heads: a warp per head
+        Q6K_DISPATCH(dtype, q6k_launch(qkv_pages_warp_kernel<T>, dim3(T_, (heads + 7) / 8), 256, 0, st, qkv, ld, splits, (size_t)split_stride, Hq, Hkv,
+                                       hd, vd, q_norm, k_norm, eps, inv_freq, inv_freq ? rotary_dim : 0, neighbours, positions, req_of_token,
+                                       block_table, max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, heads););
+        return q6k_check_launch("qkv_pages");
+    }
     Q6K_DISPATCH(dtype, q6k_launch(qkv_pages_kernel<T>, dim3(T_, heads), 128, smem, st, qkv, ld, splits, (size_t)split_stride, Hq, Hkv, hd, vd,
                                    q_norm, k_norm, eps, inv_freq, inv_freq ? rotary_dim : 0, neighbours, positions, req_of_token, block_table,
                                    max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, Hv););

@@ -49,6 +49,11 @@ struct MmaArgs {
     float* out_f32;                     // not null: the result leaves as FP32 here instead of through `out`
 };
 
+// exp and tanh on the hardware's exponential (ex2.approx): the scores here come from bfloat16 operands and the weights leave
+// as two bfloat16 terms, so 2^-21 of relative error is far below what the operands carry.  (The FP32 path has its own kernel.)
+__device__ __forceinline__ float fast_exp(float x) { return __expf(x); }
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
+
 __device__ __forceinline__ int mma_query_head(int kh, int g, int G, int maps) { return maps > 1 ? ((kh / maps) * G + g) * maps + kh % maps : kh * G + g; }
 
 __device__ __forceinline__ int first_visible_mma(int pos, int window, int chunk) {
@@ -161,6 +166,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
             for (int e = 0; e < 4; ++e) o[mb][nb][e] = 0.0f;
     }
     const int total_nb = (a.dv + 7) / 8;
+    const float inv_cap = a.softcap > 0.0f ? 1.0f / a.softcap : 0.0f;
+    // a thread's places in a key tile and a value tile (16-byte pieces, 256 apart): where 256 is a multiple of the pieces a
+    // row has, the piece's column stays and the row moves on by 256 / pieces, and no division is left in the loop
+    const int kper = dk / 8, vper = a.dv / 8;
+    const bool kfast = 256 % kper == 0, vfast = 256 % vper == 0;
+    const int k_kk0 = tid / kper, k_c8 = (tid % kper) * 8, k_step = 256 / kper;
+    const int v_kk0 = tid / vper, v_c8 = (tid % vper) * 8, v_step = 256 / vper;
     const __nv_bfloat16* kp = a.k_pages + (size_t)kh * a.k_head_stride;
     const __nv_bfloat16* vp = a.v_pages + (size_t)vh * a.v_head_stride;
 
@@ -179,15 +191,29 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
     auto fetch = [&](int buf) {
         const int* rows_of = key_rows + buf * KEYS;
         __nv_bfloat16* Kd = Kbase + buf * k_tile;
-        for (int i = tid; i < KEYS * (dk / 8); i += blockDim.x) {
-            const int kk = i / (dk / 8), c8 = (i % (dk / 8)) * 8, row = rows_of[kk];
-            cp_async16(Kd + kk * ldq + c8, kp + (size_t)(row < 0 ? 0 : row) * a.k_ld + c8, row >= 0);
+        if (kfast) {
+            for (int kk = k_kk0; kk < KEYS; kk += k_step) {
+                const int row = rows_of[kk];
+                cp_async16(Kd + kk * ldq + k_c8, kp + (size_t)(row < 0 ? 0 : row) * a.k_ld + k_c8, row >= 0);
+            }
+        } else {
+            for (int i = tid; i < KEYS * kper; i += blockDim.x) {
+                const int kk = i / kper, c8 = (i % kper) * 8, row = rows_of[kk];
+                cp_async16(Kd + kk * ldq + c8, kp + (size_t)(row < 0 ? 0 : row) * a.k_ld + c8, row >= 0);
+            }
         }
         if (!shared_v) {
             __nv_bfloat16* Vd = Vbase + buf * v_tile;
-            for (int i = tid; i < KEYS * (a.dv / 8); i += blockDim.x) {
-                const int kk = i / (a.dv / 8), c8 = (i % (a.dv / 8)) * 8, row = rows_of[kk];
-                cp_async16(Vd + kk * ldv + c8, vp + (size_t)(row < 0 ? 0 : row) * a.v_ld + c8, row >= 0);
+            if (vfast) {
+                for (int kk = v_kk0; kk < KEYS; kk += v_step) {
+                    const int row = rows_of[kk];
+                    cp_async16(Vd + kk * ldv + v_c8, vp + (size_t)(row < 0 ? 0 : row) * a.v_ld + v_c8, row >= 0);
+                }
+            } else {
+                for (int i = tid; i < KEYS * vper; i += blockDim.x) {
+                    const int kk = i / vper, c8 = (i % vper) * 8, row = rows_of[kk];
+                    cp_async16(Vd + kk * ldv + c8, vp + (size_t)(row < 0 ? 0 : row) * a.v_ld + c8, row >= 0);
+                }
             }
         }
         cp_async_commit();
@@ -249,7 +275,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
                     const int kk = warp * 8 + qc + e, j = j0 + kk;
                     const bool ok = j >= lo && j <= pos && key_row[kk] >= 0;
                     float v = ok ? s[mb][hf * 2 + e] * a.scale : -INFINITY;
-                    if (ok && a.softcap > 0.0f) v = a.softcap * tanhf(v / a.softcap);
+                    if (ok && a.softcap > 0.0f) v = a.softcap * fast_tanh(v * inv_cap);
                     s[mb][hf * 2 + e] = v;
                     mx = fmaxf(mx, v);
                 }
@@ -270,13 +296,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
 #pragma unroll
                 for (int w = 1; w < WARPS; ++w) mx = fmaxf(mx, wmax[w * ROWS + r]);
                 const float mn = fmaxf(m_run[mb][hf], mx);
-                corr[mb][hf] = (m_run[mb][hf] == -INFINITY) ? 0.0f : expf(m_run[mb][hf] - mn);
+                corr[mb][hf] = (m_run[mb][hf] == -INFINITY) ? 0.0f : fast_exp(m_run[mb][hf] - mn);
                 m_run[mb][hf] = mn;
                 float sum = 0.0f;
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const float v = s[mb][hf * 2 + e];
-                    const float p = (v == -INFINITY) ? 0.0f : expf(v - mn);
+                    const float p = (v == -INFINITY) ? 0.0f : fast_exp(v - mn);
                     sum += p;
                     s[mb][hf * 2 + e] = p;
                 }

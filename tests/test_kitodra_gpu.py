@@ -371,7 +371,7 @@ def test_a_key_far_away(tmp_path, dtype):
 
 
 # ------------------------------------------------------------------------------------------------- whole models
-LENGTHS = {"T1": [71, 130, 45, 96, 64, 33, 1, 58, 77], "T2": [85, 140, 37, 101, 2, 50, 90, 125, 44], "T3": [90, 257, 129, 48, 75, 40, 310, 66, 83],
+LENGTHS = {"T1": [71, 130, 45, 96, 64, 33, 1, 58, 77], "T2": [85, 140, 37, 101, 2, 50, 90, 125, 44], "T3": [90, 217, 129, 48, 75, 40, 150, 66, 83],
            "T4": [70, 33, 131, 20, 64, 3, 95, 41, 58]}
 
 
@@ -456,8 +456,8 @@ def test_long_decoding(model, dtype):
 def test_a_long_prompt(model, dtype):
     """A prompt of 1,100 tokens whole, in portions, and with its last tokens decoded: a recurrent state a thousand tokens old,
     windows and chunks many times over."""
-    if model["name"] not in ("T1", "T3"):
-        pytest.skip("two of the models are enough for the length (the plain implementation is slow)")
+    if model["name"] != "T1":
+        pytest.skip("one of the models is enough for the length (the plain implementation is slow)")
     reqs = {"p": helpers.random_tokens(1100, model["cfg"]["vocab"], 21)}
     for what, (steps, mt) in {"whole": helpers.schedule_whole(reqs), "portions": helpers.schedule_portions(reqs, seed=8),
                               "tail": helpers.schedule_tail(reqs, tail=40)}.items():

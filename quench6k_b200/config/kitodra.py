@@ -5,8 +5,8 @@
      "layers": [{"type": "lightning" | "attention" | "attention_2", "mixer": {...}, "mlp": {...} | null, "weights_of": j}, ...]}
 
 Every size and constant comes from the file; the layer list gives each layer's mixer and feed-forward with their own
-sizes, so no two layers need agree on anything.  A layer with `weights_of: j` has no tensors of its own: it runs with
-layer j's, on a cache and state of its own.  Mixer keys by type:
+sizes, so no two layers need agree on anything.  A layer with `weights_of: j` has no tensors of its own: it runs as
+layer j does (that layer's mixer, feed-forward, norm, sizes and constants), on a cache and state of its own.  Mixer keys by type:
   lightning:    heads, dim, vdim, decay [heads]
   attention:    heads, kv_heads, dim, vdim, scale, softcap, diff, mask {size}          (two maps per head, chunks)
   attention_2:  heads, kv_heads, dim, vdim, scale, mask {size}, rot {base, dims}       (window, values are the keys)
@@ -153,9 +153,7 @@ class KitodraConfig:
             if L.get("weights_of") is not None:
                 j = self.weights_layer(i)
                 need(self.layers[j].get("weights_of") is None, f"layer {i}: weights_of runs in a circle")
-                O = self.layers[j]
-                need(O["type"] == L["type"] and O["mixer"] == L["mixer"] and O.get("mlp") == L.get("mlp"),
-                     f"layer {i} uses layer {j}'s tensors but differs from it in type, mixer or mlp")
+                need(self.layers[j]["type"] == L["type"], f"layer {i} uses layer {j}'s tensors but differs from it in type")
         for t in self.eos_token_id:
             need(0 <= t < self.vocab, f"eos_token_id {t} outside the vocabulary")
         if self.kv_page_size is not None:

@@ -50,7 +50,7 @@ def test_config_errors_name_the_key():
     broken("T1", lambda d: d["layers"][0]["mlp"]["router"]["groups"].update(count=4), "groups")
     broken("T1", lambda d: d["layers"][0]["mlp"]["router"].update(top=5), "kept groups")
     broken("T1", lambda d: d["layers"][3].update(weights_of=9), "weights_of")
-    broken("T1", lambda d: d["layers"][3].update(weights_of=0), "differs")
+    broken("T1", lambda d: d["layers"][3].update(weights_of=0), "differs")            # a window layer cannot run a lightning layer's tensors
     broken("T1", lambda d: (d["layers"][0].update(weights_of=4), d["layers"][4].update(weights_of=0)), "circle")
     broken("T1", lambda d: d["embedding"]["bigram"].pop("buckets"), "buckets")
     broken("T1", lambda d: d.pop("norm"), "norm")

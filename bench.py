@@ -407,7 +407,7 @@ def kitodra_config(size):
     win = {"type": "attention_2", "mlp": moe, "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                                                          "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 64}}}
     diff = {"type": "attention", "mlp": moe, "mixer": {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 30.0,
-                                                        "diff": 0.5, "mask": {"size": window}}}
+                                                        "diff": 0.4, "mask": {"size": window}}}
     layers = [light, win, diff, dict(light)]
     layers += [dict(L, weights_of=i) for i, L in enumerate(layers)]
     return {"architecture": "Kitodra", "vocab": 32768, "width": D, "norm": {"eps": 1e-6}, "kv_page_size": 16,

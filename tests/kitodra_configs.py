@@ -71,10 +71,10 @@ def _t3():
     # widths at which the bfloat16 path takes its tensor-core products and attention kernels
     L = [sink(4, 2, 64, 0.1, 100, 32, 50000.0, ff(8, 2, 64, 1.0, groups=(2, 1), shared=(128, 1.5))),
          lightning(4, 64, 64, [0.95, 0.99, 0.995, 0.999], ff(16, 4, 32, 1.3, groups=(4, 2), shared=(64, 1.0))),
-         difference(4, 2, 32, 64, 0.15, 48, 20.0, 0.5, ff(8, 2, 64, 0.9, groups=(8, 3))),
+         difference(4, 2, 32, 64, 0.15, 48, 25.0, 0.45, ff(8, 2, 64, 0.9, groups=(8, 3))),
          sink(8, 8, 128, 0.08, 200, 128, 1e6, ff(4, 2, 96, 1.0, shared=(32, 2.0))),
          lightning(2, 128, 128, [0.98, 0.9995])]
-    return model(L + [again(L, 2), again(L, 0)], width=128, vocab=384, page=16, bigram=(509, 1000003, 99991))
+    return model(L + [again(L, 2), again(L, 0)], width=128, vocab=384, page=16, bigram=(521, 1000003, 99991))
 
 
 def _t4():

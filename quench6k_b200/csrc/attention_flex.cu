@@ -269,12 +269,14 @@ __device__ __forceinline__ float rotated(const float* x, int d, int rd, int neig
 // qkv: FP32 [T, ld] = [Hq heads of hd | Hkv heads of hd | Hv heads of vd].  Per-head RMS norm of q and k (weights or
 // null), rotation of their first rd dimensions (inv_freq or null), q -> q_out [T, Hq, hd]; k, v -> pages
 // [Hkv, num_pages, page_size, hd] and [Hv, .., vd].  Grid (T, Hq + Hkv + Hv) (or (T, Hq) when nothing is written).
+// bias: one entry per column of a row, added to the summed slices, or null.  v_is_k: the rows hold no v heads; a value is its
+// key as projected (bias included, before norm and rotation).
 template <typename T>
 __global__ void __launch_bounds__(128) qkv_pages_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, int hd, int vd,
                                                         const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rd,
                                                         int neighbours, const int* positions, const int* req_of_token,
                                                         const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out,
-                                                        T* k_pages, T* v_pages, int Hv) {
+                                                        T* k_pages, T* v_pages, int Hv, const float* bias, int v_is_k) {
     pdl_enter();
     extern __shared__ float xs[];            // max(hd, vd) floats
     __shared__ float red[32];
@@ -282,13 +284,16 @@ __global__ void __launch_bounds__(128) qkv_pages_kernel(const float* qkv, int ld
     const int kind = h < Hq ? 0 : h < Hq + Hkv ? 1 : 2;
     const int pos = positions[t];
     const int n = kind == 2 ? vd : hd;
+    // a value head of a layer whose values are its keys reads the key head of its number (as projected)
     const size_t col = kind == 0 ? (size_t)h * hd : kind == 1 ? (size_t)Hq * hd + (size_t)(h - Hq) * hd
-                                                              : (size_t)(Hq + Hkv) * hd + (size_t)(h - Hq - Hkv) * vd;
+                     : v_is_k    ? (size_t)Hq * hd + (size_t)(h - Hq - Hkv) * hd
+                                 : (size_t)(Hq + Hkv) * hd + (size_t)(h - Hq - Hkv) * vd;
     const float* src = qkv + (size_t)t * ld + col;
     float ss = 0.0f;
     for (int d = threadIdx.x; d < n; d += blockDim.x) {
         float v = src[d];
         for (int s = 1; s < splits; ++s) v += src[s * split_stride + d];
+        if (bias) v += bias[col + d];
         xs[d] = v;
         ss = fmaf(v, v, ss);
     }
@@ -320,7 +325,7 @@ __global__ void __launch_bounds__(256) qkv_pages_warp_kernel(const float* qkv, i
                                                              const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rd,
                                                              int neighbours, const int* positions, const int* req_of_token,
                                                              const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out,
-                                                             T* k_pages, T* v_pages, int heads) {
+                                                             T* k_pages, T* v_pages, int heads, const float* bias, int v_is_k) {
     pdl_enter();
     __shared__ float stage[8][256];
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -329,8 +334,10 @@ __global__ void __launch_bounds__(256) qkv_pages_warp_kernel(const float* qkv, i
     const int kind = h < Hq ? 0 : h < Hq + Hkv ? 1 : 2;
     const int pos = positions[t];
     const int n = kind == 2 ? vd : hd;
+    // a value head of a layer whose values are its keys reads the key head of its number (as projected)
     const size_t col = kind == 0 ? (size_t)h * hd : kind == 1 ? (size_t)Hq * hd + (size_t)(h - Hq) * hd
-                                                              : (size_t)(Hq + Hkv) * hd + (size_t)(h - Hq - Hkv) * vd;
+                     : v_is_k    ? (size_t)Hq * hd + (size_t)(h - Hq - Hkv) * hd
+                                 : (size_t)(Hq + Hkv) * hd + (size_t)(h - Hq - Hkv) * vd;
     const float* src = qkv + (size_t)t * ld + col;
     float x[8];
     float ss = 0.0f;
@@ -341,6 +348,7 @@ __global__ void __launch_bounds__(256) qkv_pages_warp_kernel(const float* qkv, i
         if (d < n) {
             v = src[d];
             for (int s = 1; s < splits; ++s) v += src[s * split_stride + d];
+            if (bias) v += bias[col + d];
         }
         x[j] = v;
         ss = fmaf(v, v, ss);
@@ -505,9 +513,11 @@ Q6K_API int q6k_attention_flex(const float* qa, int da, const void* qb, int db, 
 Q6K_API int q6k_qkv_pages(const float* qkv, int ld, int splits, long long split_stride, int T_, int Hq, int Hkv, int hd, int vd,
                           const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rotary_dim, int neighbours,
                           const int* positions, const int* req_of_token, const int* block_table, int max_blocks, int page_size,
-                          int num_pages, void* q_out, void* k_pages, void* v_pages, int write_kv, int dtype, int Hv, cudaStream_t st) {
+                          int num_pages, void* q_out, void* k_pages, void* v_pages, int write_kv, int dtype, int Hv, const float* bias, int v_is_k,
+                          cudaStream_t st) {
     if (T_ == 0) return 0;
     if (Hv <= 0) Hv = Hkv;
+    Q6K_REQUIRE(!v_is_k || (Hv == Hkv && vd == hd), "qkv_pages: values that are the keys have the keys' heads and width");
     Q6K_REQUIRE(T_ > 0 && Hq > 0 && Hkv > 0 && hd > 0 && vd > 0 && splits >= 1, "qkv_pages: bad sizes T=%d Hq=%d Hkv=%d hd=%d vd=%d", T_, Hq, Hkv, hd, vd);
     Q6K_REQUIRE(!inv_freq || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= hd), "qkv_pages: %d rotating dimensions of a head of %d", rotary_dim, hd);
     Q6K_REQUIRE(!write_kv || (page_size > 0 && max_blocks > 0), "qkv_pages: bad page_size %d / max_blocks %d", page_size, max_blocks);
@@ -518,12 +528,12 @@ Q6K_API int q6k_qkv_pages(const float* qkv, int ld, int splits, long long split_
     if (hd <= 256 && vd <= 256 && (heads + 7) / 8 <= 65535) {                 // narrow heads: a warp per head
         Q6K_DISPATCH(dtype, q6k_launch(qkv_pages_warp_kernel<T>, dim3(T_, (heads + 7) / 8), 256, 0, st, qkv, ld, splits, (size_t)split_stride, Hq, Hkv,
                                        hd, vd, q_norm, k_norm, eps, inv_freq, inv_freq ? rotary_dim : 0, neighbours, positions, req_of_token,
-                                       block_table, max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, heads););
+                                       block_table, max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, heads, bias, v_is_k););
         return q6k_check_launch("qkv_pages");
     }
     Q6K_DISPATCH(dtype, q6k_launch(qkv_pages_kernel<T>, dim3(T_, heads), 128, smem, st, qkv, ld, splits, (size_t)split_stride, Hq, Hkv, hd, vd,
                                    q_norm, k_norm, eps, inv_freq, inv_freq ? rotary_dim : 0, neighbours, positions, req_of_token, block_table,
-                                   max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, Hv););
+                                   max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, Hv, bias, v_is_k););
     return q6k_check_launch("qkv_pages");
 }
 

@@ -20,7 +20,8 @@ namespace {
 template <typename T>
 __global__ void qk_prep_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
                                float eps, const float* inv_freq, int rd, int neighbours, const int* positions, const int* req_of_token,
-                               const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out, T* k_pages, T* v_pages) {
+                               const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out, T* k_pages, T* v_pages,
+                               const float* bias, int v_is_k) {
     pdl_enter();
     extern __shared__ float xs[];            // hd floats
     __shared__ float red[32];
@@ -30,8 +31,11 @@ __global__ void qk_prep_kernel(const float* qkv, int ld, int splits, size_t spli
     const bool live = d < hd;
     const float* src = qkv + (size_t)t * ld + (is_q ? h * hd : (Hq + (h - Hq)) * hd);
     float x = 0.0f;
-    if (live)
+    if (live) {
         for (int s = 0; s < splits; ++s) x += src[s * split_stride + d];        // split-K partials, in order
+        if (bias) x += bias[(is_q ? h * hd : (Hq + (h - Hq)) * hd) + d];
+    }
+    const float projected = x;               // the key as projected: the value of a layer whose values are its keys
     const float* nw = is_q ? q_norm : k_norm;
     if (nw) {
         const float ss = block_sum(x * x, red);
@@ -59,8 +63,12 @@ __global__ void qk_prep_kernel(const float* qkv, int ld, int splits, size_t spli
         if (page < 0) return;                 // no page behind this position: nothing is written
         const size_t row = (((size_t)kh * num_pages + page) * page_size + pos % page_size) * hd + d;
         k_pages[row] = from_f32<T>(x);
-        float v = 0.0f;
-        for (int s = 0; s < splits; ++s) v += qkv[s * split_stride + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd + d];
+        float v = projected;
+        if (!v_is_k) {
+            v = 0.0f;
+            for (int s = 0; s < splits; ++s) v += qkv[s * split_stride + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd + d];
+            if (bias) v += bias[(size_t)(Hq + Hkv + kh) * hd + d];
+        }
         v_pages[row] = from_f32<T>(v);
     }
 }
@@ -75,7 +83,7 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
                                                            const float* k_norm, float eps, const float* inv_freq, int rd, int neighbours,
                                                            const int* positions, const int* req_of_token, const int* block_table,
                                                            int max_blocks, int page_size, int num_pages, T* q_out, T* k_pages,
-                                                           T* v_pages, int heads) {
+                                                           T* v_pages, int heads, const float* bias, int v_is_k) {
     pdl_enter();
     constexpr int hd = EPL * 32, half = hd / 2;
     __shared__ float rot_cos[half], rot_sin[half];
@@ -93,14 +101,25 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
         x[i] = valid ? src[lane + 32 * i] : 0.0f;
-        v[i] = writes_kv ? vsrc[lane + 32 * i] : 0.0f;
+        v[i] = writes_kv && !v_is_k ? vsrc[lane + 32 * i] : 0.0f;
     }
     for (int s = 1; s < splits; ++s) {                                               // split-K partials, in order
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
             if (valid) x[i] += src[s * split_stride + lane + 32 * i];
-            if (writes_kv) v[i] += vsrc[s * split_stride + lane + 32 * i];
+            if (writes_kv && !v_is_k) v[i] += vsrc[s * split_stride + lane + 32 * i];
         }
+    }
+    if (bias) {                                                                      // the projections' biases, columns as the row's
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            if (valid) x[i] += bias[(size_t)h * hd + lane + 32 * i];
+            if (writes_kv && !v_is_k) v[i] += bias[(size_t)(Hq + Hkv + kh) * hd + lane + 32 * i];
+        }
+    }
+    if (v_is_k) {                                                                    // the values are the keys as projected
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) v[i] = x[i];
     }
     const int page = writes_kv ? block_table[(size_t)req * max_blocks + pos / page_size] : -1;
     if (inv_freq) {
@@ -170,10 +189,12 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
 // (neighbours == 0: d with d + rotary_dim/2) or by neighbours (2i with 2i + 1).
 // write_kv == 0: only q is produced (the layer reads a cache another layer wrote).
 // splits > 1: qkv is [splits, T, ld] (slices split_stride floats apart) and the slices are summed in order first.
+// bias: FP32, one entry per column of a row (q, k, v side by side), added to the summed slices, or null.  v_is_k: a key's value
+// is the key itself as projected (bias included, before norm and rotation); the rows then hold no v heads.
 Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_stride, int T_, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
                         float eps, const float* inv_freq, int rotary_dim, int neighbours, const int* positions, const int* req_of_token,
                         const int* block_table, int max_blocks, int page_size, int num_pages, void* q_out, void* k_pages,
-                        void* v_pages, int write_kv, int dtype, cudaStream_t st) {
+                        void* v_pages, int write_kv, int dtype, const float* bias, int v_is_k, cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && Hq > 0 && Hkv > 0 && hd > 0, "qk_prep: bad sizes T=%d Hq=%d Hkv=%d hd=%d", T_, Hq, Hkv, hd);
     Q6K_REQUIRE(splits >= 1, "qk_prep: bad split count %d", splits);
@@ -187,7 +208,7 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_st
         Q6K_REQUIRE(wgrid.y <= 65535, "qk_prep: %d heads exceed the grid limit", heads);
 #define WARP_LAUNCH(EPL)                                                                                                    \
     q6k_launch(qk_prep_warp_kernel<T, EPL>, wgrid, 256, 0, st, qkv, ld, splits, (size_t)split_stride, Hq, Hkv, q_norm, k_norm, eps, inv_freq, rd, neighbours, positions, req_of_token, \
-                                                       block_table, max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, heads)
+                                                       block_table, max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, heads, bias, v_is_k)
         Q6K_DISPATCH(dtype, {
             if (hd == 64) WARP_LAUNCH(2);
             else if (hd == 128) WARP_LAUNCH(4);
@@ -200,6 +221,6 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_st
     dim3 grid(T_, heads);
     Q6K_DISPATCH(dtype, q6k_launch(qk_prep_kernel<T>, grid, threads, hd * sizeof(float), st, 
                             qkv, ld, splits, (size_t)split_stride, Hq, Hkv, hd, q_norm, k_norm, eps, inv_freq, rd, neighbours, positions, req_of_token, block_table,
-                            max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages););
+                            max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, bias, v_is_k););
     return q6k_check_launch("qk_prep");
 }

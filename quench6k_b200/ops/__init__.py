@@ -562,8 +562,11 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = N
 # --------------------------------------------------------------------------- attention
 def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: float, rotary,
             positions: torch.Tensor, req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int,
-            k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+            k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
+            values_are_keys: bool = False) -> torch.Tensor:
     """QK-norm, rotation, q -> out_dtype [T, Hq, hd]; k, v -> their pages (when k_pages is given).
+    bias: FP32, one entry per column of a row (q, k, v side by side), added to the summed product first.  values_are_keys:
+    the rows hold q and k only, and a key's value is the key as projected (bias included, before norm and rotation).
     rotary: None, or (inv_freq float32 [rotary_dim / 2] on the device, rotary_dim, neighbours): the
     first rotary_dim dimensions of every q and k head turn by position * inv_freq[pair], paired by
     halves (d with d + rotary_dim / 2) or, neighbours=True, 2i with 2i + 1.
@@ -574,8 +577,12 @@ def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: 
         splits, split_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
         qkv = qkv[0]
     T = qkv.shape[0]
-    if qkv.shape[1] < (Hq + 2 * Hkv) * hd and k_pages is not None:
+    if qkv.shape[1] < (Hq + (1 if values_are_keys else 2) * Hkv) * hd and k_pages is not None:
         raise KernelError("qk_prep: qkv rows are too short")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() < (Hq + (0 if k_pages is None else Hkv if values_are_keys else 2 * Hkv)) * hd:
+            raise KernelError("qk_prep: the bias is shorter than a row")
     _need(positions, "positions", torch.int32)
     _need(req_of_token, "req_of_token", torch.int32)
     write = k_pages is not None
@@ -598,7 +605,7 @@ def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: 
     _call("q6k_qk_prep", _ptr(qkv), _i(qkv.stride(0)), _i(splits), _ll(split_stride), _i(T), _i(Hq), _i(Hkv), _i(hd), _ptr(q_norm), _ptr(k_norm), _f(eps),
           _ptr(inv_freq), _i(rotary_dim), _i(1 if neighbours else 0), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
           _i(max_blocks), _i(page_size), _i(k_pages.shape[1] if write else 0), _ptr(q), _ptr(k_pages), _ptr(v_pages),
-          _i(1 if write else 0), _i(dtype_code(out_dtype)), _stream())
+          _i(1 if write else 0), _i(dtype_code(out_dtype)), _ptr(bias), _i(1 if values_are_keys else 0), _stream())
     return q
 
 
@@ -1138,10 +1145,16 @@ def selective_scan_segments(q_lens, device):
 
 def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_norm, eps: float, rotary, positions: torch.Tensor,
               req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int, k_pages: Optional[torch.Tensor],
-              v_pages: Optional[torch.Tensor], out_dtype: torch.dtype, v_heads: Optional[int] = None) -> torch.Tensor:
+              v_pages: Optional[torch.Tensor], out_dtype: torch.dtype, v_heads: Optional[int] = None, bias: Optional[torch.Tensor] = None,
+              values_are_keys: bool = False) -> torch.Tensor:
     """qk_prep for keys and values of different widths: qkv FP32 [T, Hq hd + Hkv hd + Hv vd] (or split-K slices of it);
-    q -> [T, Hq, hd]; k -> pages [Hkv, P, page, hd]; v -> pages [Hv, P, page, vd].  v_heads: Hv, if it is not Hkv."""
+    q -> [T, Hq, hd]; k -> pages [Hkv, P, page, hd]; v -> pages [Hv, P, page, vd].  v_heads: Hv, if it is not Hkv.
+    bias: FP32, one entry per column of a row, added to the summed product first.  values_are_keys: the rows hold q and k
+    only, and a key's value is the key as projected (bias included, before norm and rotation)."""
     Hv = v_heads or Hkv
+    v_cols = 0 if values_are_keys else Hv * vd
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
     _need(qkv, "qkv", torch.float32)
     splits, split_stride = 1, 0
     if qkv.dim() == 3:
@@ -1156,7 +1169,7 @@ def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_
         if (tuple(k_pages.shape[2:]) != (page_size, hd) or tuple(v_pages.shape[2:]) != (page_size, vd) or k_pages.shape[0] != Hkv
                 or v_pages.shape[0] != Hv or v_pages.shape[1] != k_pages.shape[1]):
             raise KernelError("qkv_pages: the pages do not match the heads")
-    if qkv.shape[1] < Hq * hd + (Hkv * hd + Hv * vd if write else 0):
+    if qkv.shape[1] < Hq * hd + (Hkv * hd + v_cols if write else 0) or (bias is not None and bias.numel() < Hq * hd + (Hkv * hd + v_cols if write else 0)):
         raise KernelError("qkv_pages: qkv rows are too short")
     inv_freq, rotary_dim, neighbours = rotary if rotary is not None else (None, 0, False)
     q = torch.empty((T, Hq, hd), dtype=out_dtype, device=qkv.device)
@@ -1164,7 +1177,7 @@ def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_
           _ptr(k_norm), _f(eps), _ptr(inv_freq), _i(rotary_dim), _i(1 if neighbours else 0), _ptr(positions), _ptr(req_of_token),
           _ptr(block_table), _i(block_table.shape[1] if block_table is not None else 1), _i(page_size),
           _i(k_pages.shape[1] if write else 0), _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(1 if write else 0),
-          _i(dtype_code(out_dtype)), _i(Hv), _stream())
+          _i(dtype_code(out_dtype)), _i(Hv), _ptr(bias), _i(1 if values_are_keys else 0), _stream())
     return q
 
 

@@ -13,8 +13,9 @@ slot so that a prompt may be cut anywhere.
 Further options, each a parameter: a bias on the output projection (`o_bias`); a sink of a fixed score instead of learned
 ones (`fixed_sink`: a sink of 0 adds one to every softmax denominator); q/k norms without stored weights
 (`qk_norm_weight=False`: the vectors are divided by their root mean square, which commutes with the rotation); values that
-are the projected keys themselves, before norm and rotation (`values_are_keys`: no value projection is stored; the stacked
-product carries the key rows twice, so everything downstream finds [q | k | v] as usual); a cap on the scaled scores
+are the projected keys themselves, before norm and rotation (`values_are_keys`: no value projection is stored and the
+stacked product has q and k only; the kernels that write the pages store the key, as it stands before its norm, as the
+value); a cap on the scaled scores
 (`softcap`: s -> c tanh(s / c)); and difference attention (`maps=2` with `diff`): every head attends twice, with queries
 and keys of its own per map (q and k hold a head's maps side by side, the q/k norm weights are shared by all heads and
 maps) over the same values, and the head's result is o = a1 - L a2 divided by its root mean square over the value
@@ -61,6 +62,8 @@ class Attention(Mixer):
             raise ValueError("learned sinks and a fixed sink exclude each other")
         if self.values_are_keys and (self.vd != head_dim or self.maps > 1 or conv):
             raise ValueError("values that are the keys have the keys' width, one map and no convolution")
+        if self.values_are_keys and self.pos.rotary_table() is None and not self.pos.is_identity:
+            raise ValueError("values that are the keys take a rotation of pairs or no position encoding")
         if self.talk and (sinks or fixed_sink is not None or self.maps > 1 or self.softcap):
             raise ValueError("mixed heads are combined with neither sinks, maps nor a cap on the scores")
         self.flexible = (self.vd != head_dim or self.chunk is not None or self.talk or self.maps > 1 or self.softcap > 0.0
@@ -80,7 +83,8 @@ class Attention(Mixer):
                       "v_bias": "v_proj.bias", "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight",
                       "o_bias": "o_proj.bias", "lq1": "lambda_q1", "lk1": "lambda_k1", "lq2": "lambda_q2", "lk2": "lambda_k2", **(names or {})}
         # rows of the stacked projection: a head's maps side by side in q and k, one value head per KV head
-        self.nq, self.nk, self.nv = num_heads * self.maps * head_dim, num_kv_heads * self.maps * head_dim, num_kv_heads * self.vd
+        self.nq, self.nk = num_heads * self.maps * head_dim, num_kv_heads * self.maps * head_dim
+        self.nv = 0 if self.values_are_keys else num_kv_heads * self.vd
 
     def tensors(self):
         D, Hq, Hkv, hd, n = self.D, self.Hq, self.Hkv, self.hd, self.names
@@ -112,9 +116,9 @@ class Attention(Mixer):
         # q, k and v rows stacked so one product yields [q | k | v] per token: each piece is copied into its place
         # on the device as it arrives, so that no two copies of the three are held at once
         nq, nk, nv, n = self.nq, self.nk, self.nv, self.names
-        v_from = "k" if self.values_are_keys else "v"          # values that are the keys: the key rows once more
+        pieces = ("q", "k") if self.values_are_keys else ("q", "k", "v")
         self.w_qkv = torch.empty((nq + nk + nv, self.D), dtype=rt.dtype, device=rt.device)
-        for name, lo, hi in ((n["q"], 0, nq), (n["k"], nq, nq + nk), (n[v_from], nq + nk, nq + nk + nv)):
+        for name, lo, hi in ((n["q"], 0, nq), (n["k"], nq, nq + nk), (n["v"], nq + nk, nq + nk + nv))[:len(pieces)]:
             self.w_qkv[lo:hi].copy_(get(name))
         self.w_q = self.w_qkv[:nq]
         self.w_o = to_operand(get(n["o"]), rt)
@@ -129,7 +133,10 @@ class Attention(Mixer):
             self.sinks = torch.full((self.Hq,), float(self.fixed_sink), dtype=torch.float32, device=rt.device)
         self.w_talk = to_f32(get(n["talk"]), rt) if self.talk else None
         # biases and taps of q, k and v side by side, like the rows of the stacked product
-        self.bias = torch.cat([to_f32(get(n[x + "_bias"]), rt) for x in ("q", "k", v_from)]).contiguous() if self.has_bias else None
+        self.bias = torch.cat([to_f32(get(n[x + "_bias"]), rt) for x in pieces]).contiguous() if self.has_bias else None
+        # biases without a convolution are added by the kernel that normalises q and k and writes the pages (an encoding that
+        # is no rotation of pairs has no such kernel in front of it: its biases take the convolution kernel with one tap)
+        self.prep_bias = self.bias if self.has_bias and not self.taps and (self.flexible or self.pos.rotary_table() is not None or self.pos.is_identity) else None
         if self.has_o_bias:
             self.o_bias = to_f32(get(n["o_bias"]), rt)
             self._one_tap = torch.ones((self.D, 1), dtype=torch.float32, device=rt.device)
@@ -139,7 +146,7 @@ class Attention(Mixer):
             # FP32 throughout, as a model holds it: two dot products, two exponentials, one difference
             self.map_weight = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum()) + torch.tensor(self.diff, dtype=torch.float32))
         self.conv_w = torch.cat([to_f32(get(n[x + "_conv"]), rt) for x in "qkv"]).contiguous() if self.taps else None
-        if self.has_bias and not self.taps:                         # a bias alone: one tap of weight one
+        if self.has_bias and not self.taps and self.prep_bias is None:          # a bias alone: one tap of weight one
             self.conv_w = torch.ones((nq + nk + nv, 1), dtype=torch.float32, device=rt.device)
         self._no_tail = torch.zeros((1, 0, nq + nk + nv), dtype=torch.float32, device=rt.device)
         self.pos.bind(lambda name: get("position." + name), rt)
@@ -178,7 +185,7 @@ class Attention(Mixer):
         M = self.maps
         q = ops.qkv_pages(qkv, self.Hq * M, self.Hkv * M, self.hd, self.vd, self.q_norm, self.k_norm, self.eps, self.pos.rotary_table(),
                           ctx.positions, ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
-                          cache.v if write else None, rt.dtype, v_heads=self.Hkv)
+                          cache.v if write else None, rt.dtype, v_heads=self.Hkv, bias=self.prep_bias, values_are_keys=self.values_are_keys)
         ops.current_tag = "attention.keys"
         tiles = None if rt.is_fp32 or not rt.tensor_cores else ctx.query_tiles(ops.attention_flex_tile_tokens(self.Hq, self.Hkv))
         a = ops.attention_flex(None, q.view(-1, self.hd), False, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.Hq * M,
@@ -214,7 +221,8 @@ class Attention(Mixer):
         fused_pos = rotary is not None or self.pos.is_identity
         # a step of a few tokens per request: the kernel that splits the keys normalises and rotates q itself and makes
         # the new keys and values (one launch less)
-        in_attention = (self.prepare_in_attention and how[0] == "split" and fused_pos and self.conv_w is None and
+        in_attention = (self.prepare_in_attention and how[0] == "split" and fused_pos and self.conv_w is None and self.prep_bias is None and
+                        not self.values_are_keys and
                         ops.attention_mma_prepares(self.hd, self.Hq // self.Hkv, how[1][0], rotary[1] if rotary else 0, bool(rotary and rotary[2])))
         # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which the next kernel sums
         ops.current_tag = "attention.qkv"
@@ -236,7 +244,7 @@ class Attention(Mixer):
         else:
             q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, self.q_norm, self.k_norm, self.eps, rotary, ctx.positions,
                             ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
-                            cache.v if write else None, rt.dtype)
+                            cache.v if write else None, rt.dtype, bias=self.prep_bias, values_are_keys=self.values_are_keys)
         ops.current_tag = "attention.keys"
         a = self._attend(q, cache, table, ctx, how)
         # the block adds it into the stream inside its next norm (which also sums split-K partials)

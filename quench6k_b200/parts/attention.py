@@ -13,7 +13,7 @@ slot so that a prompt may be cut anywhere.
 Further options, each a parameter: a bias on the output projection (`o_bias`); a sink of a fixed score instead of learned
 ones (`fixed_sink`: a sink of 0 adds one to every softmax denominator); q/k norms without stored weights
 (`qk_norm_weight=False`: the vectors are divided by their root mean square, which commutes with the rotation); values that
-are the projected keys themselves, before norm and rotation (`values_are_keys`: no value projection is stored and the
+are the key projection's raw results (`values_are_keys`: no value projection is stored and the
 stacked product has q and k only; the kernels that write the pages store the key, as it stands before its norm, as the
 value); a cap on the scaled scores
 (`softcap`: s -> c tanh(s / c)); and difference attention (`maps=2` with `diff`): every head attends twice, with queries

@@ -93,9 +93,10 @@ def difference_attention(h, w, m, eps):
 
 
 def sink_attention(h, w, m, eps, sink=True):
-    """Softmax attention in a sliding window whose denominator holds one more term of score zero; the values are the
-    projected keys (before rotation and norm); q and k are rotated over their first dims entries, then divided by their root
-    mean square.  sink=False leaves the extra term out (for tests that ask whether it would show)."""
+    """Softmax attention in a sliding window whose denominator holds one more term of score zero.  There is no value
+    projection: what the weights are applied to is the key projection's raw result.  q and k turn over their first dims
+    entries and are then brought to unit root mean square.  sink=False leaves the extra term out (for tests that ask
+    whether it would show)."""
     T = h.shape[0]
     H, G, d, win = m["heads"], m["kv_heads"], m["dim"], m["mask"]["size"]
     pos = torch.arange(T)
